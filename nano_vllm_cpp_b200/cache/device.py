@@ -34,6 +34,12 @@ class CacheView:
         return CacheView(self.kind, self.group, self.k, self.v, self.state, False, self.page_size, parts)
 
 
+def _group_key(spec: KVCacheSpec):
+    """What layers must share to share page ids: the window, and with a window the number of first positions that
+    stay readable behind it."""
+    return (spec.window, spec.keep_first) if spec.window > 0 and spec.keep_first > 0 else spec.window
+
+
 def _leaves(spec):
     """The page and state specs inside a cache spec, composites opened, in order."""
     if isinstance(spec, CompositeCacheSpec):
@@ -47,17 +53,17 @@ class DeviceCache:
     def __init__(self, cache_specs: list, page_size: int, max_slots: int, device, dtype):
         self.page_size, self.device, self.dtype, self.max_slots = page_size, device, dtype, max_slots
         self.specs = cache_specs
-        self.windows: list = []                    # one per group
+        self.windows: list = []                    # one per group: the window, or (window, kept first positions)
         for s in cache_specs:
             for leaf in _leaves(s):
-                if isinstance(leaf, KVCacheSpec) and leaf.window not in self.windows:
-                    self.windows.append(leaf.window)
+                if isinstance(leaf, KVCacheSpec) and _group_key(leaf) not in self.windows:
+                    self.windows.append(_group_key(leaf))
         self.views: list = []
         self.num_pages: list = []
         self.state_buffers: dict = {}              # dtype -> [slots, words of that dtype]
 
     def _group(self, spec: KVCacheSpec) -> int:
-        return self.windows.index(spec.window)
+        return self.windows.index(_group_key(spec))
 
     def bytes_per_page(self) -> list:
         """Per group: bytes of one page over all its entries."""
@@ -66,7 +72,8 @@ class DeviceCache:
         for s in self.specs:
             for leaf in _leaves(s):
                 if isinstance(leaf, KVCacheSpec):
-                    out[self._group(leaf)] += leaf.num_kv_heads * self.page_size * (leaf.head_dim + leaf.value_dim) * item
+                    per_token = leaf.head_dim + (leaf.value_dim if leaf.values else 0)
+                    out[self._group(leaf)] += leaf.num_kv_heads * self.page_size * per_token * item
         return out
 
     def state_bytes_per_slot(self) -> int:
@@ -117,7 +124,9 @@ class DeviceCache:
             g = self._group(s)
             pages = max(1, self.num_pages[g])
             k = torch.zeros((pages, s.num_kv_heads, self.page_size, s.head_dim), dtype=self.dtype, device=self.device)
-            v = torch.zeros((pages, s.num_kv_heads, self.page_size, s.value_dim), dtype=self.dtype, device=self.device)
+            v = None            # (a layer whose values are read where its keys are keeps one array)
+            if s.values:
+                v = torch.zeros((pages, s.num_kv_heads, self.page_size, s.value_dim), dtype=self.dtype, device=self.device)
             return CacheView("kv", g, k, v, None, True, self.page_size)
         if isinstance(s, StateCacheSpec):
             at, n = next(places)

@@ -2,8 +2,9 @@
 
 The class lives in native code (csrc/host_core.cpp, ``CacheManager``); this is its Python face.
 Layers with the same needs form a *group* with pages and block tables of its own: one group for
-layers that read every earlier key, one for each window size.  A group with a window gives a
-page back as soon as every position in it lies before the window of the next row to run.  A
+layers that read every earlier key, one for each window size (and number of first positions that stay
+readable behind the window).  A group with a window gives a page back as soon as every position in it lies
+before the window of the next row to run, unless the page holds one of the kept first positions.  A
 request also holds one *state slot* (an index into fixed-size per-request arrays) from ``open``
 to ``close``.
 
@@ -68,21 +69,24 @@ class RequestCache:
 class CacheManager:
     def __init__(self, windows: list, num_pages, page_size: int, max_requests: int,
                  prefix_caching: bool = False, has_state: bool = False):
-        """``windows``: one entry per group (0 = reads every key); it may be empty for a model without paged
+        """``windows``: one entry per group (0 = reads every key; ``(window, keep_first)`` for a window behind which
+        the first ``keep_first`` positions stay readable); it may be empty for a model without paged
         layers, whose requests hold a state slot and nothing else.  ``num_pages``: an int for all groups or a
         list.  ``has_state``: some layer keeps a fixed-size state per request; prefix sharing is then refused
         (a request that adopted another's pages would skip tokens its state never saw)."""
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(windows)
-        self.windows = list(windows)
+        self.keeps = [int(w[1]) if isinstance(w, (tuple, list)) else 0 for w in windows]
+        self.windows = [int(w[0]) if isinstance(w, (tuple, list)) else int(w) for w in windows]
         self.page_size = page_size
         self.max_requests = max_requests
         self.num_groups = len(windows)
         w, _ = host.ints(self.windows)
         n, _ = host.ints(list(num_pages))
+        k, _ = host.ints(self.keeps)
         L = host.lib()
         self._h = L.nvh_manager_create(w, n, self.num_groups, page_size, max_requests, 1 if prefix_caching else 0,
-                                       1 if has_state else 0)
+                                       1 if has_state else 0, k)
         self.pools = [BlockPool(num_pages[g], page_size, _handle=L.nvh_manager_pool(self._h, g))
                       for g in range(self.num_groups)]
         self.prefix_caching = bool(L.nvh_manager_prefix_caching(self._h))

@@ -148,8 +148,9 @@ class BlockPool {
 // ------------------------------------------------------------------------------------------ CacheManager
 // Which pages and which state slot every live request holds.  Layers with the same needs form a group
 // with pages and block tables of its own (one group for layers that read every earlier key, one per
-// window size); a group with a window gives a page back as soon as every position in it lies before
-// the window of the next row to run.  A request also holds one state slot from open to close.  Hashing
+// window size and number of kept first positions); a group with a window gives a page back as soon as every
+// position in it lies before the window of the next row to run, except the pages that hold one of the group's kept
+// first positions, which a request holds to its end.  A request also holds one state slot from open to close.  Hashing
 // of full pages, so that requests with a common prefix share them (src/block_manager.cpp:56-98,
 // 121-134), is offered only for a single group without a window.
 struct RequestCache {
@@ -166,6 +167,7 @@ struct RequestCache {
 class CacheManager {
  public:
   std::vector<int> windows;
+  std::vector<int> keeps;                 // per group: the first so many positions stay readable behind the window
   int page_size, max_requests;
   std::vector<BlockPool> pools;
   std::vector<int> free_slots;            // a stack: slot 0 is handed out first
@@ -176,8 +178,10 @@ class CacheManager {
   // seen every token of its request, so a request must never skip tokens that another request's pages hold:
   // prefix sharing is refused then, as it is for more than one group or a window.  `groups` may be 0 (a model
   // without paged layers): requests then hold a state slot and nothing else.
-  CacheManager(const int* w, const int* n_pages, int groups, int ps, int max_req, bool prefix, bool has_state)
-      : windows(w, w + groups), page_size(ps), max_requests(max_req) {
+  CacheManager(const int* w, const int* n_pages, int groups, int ps, int max_req, bool prefix, bool has_state,
+               const int* keep = nullptr)
+      : windows(w, w + groups), keeps(groups, 0), page_size(ps), max_requests(max_req) {
+    if (keep) keeps.assign(keep, keep + groups);
     for (int g = 0; g < groups; ++g) pools.emplace_back(n_pages[g], ps);
     for (int s = max_req - 1; s >= 0; --s) free_slots.push_back(s);
     prefix_caching = prefix && !has_state && groups == 1 && windows[0] == 0;
@@ -214,10 +218,13 @@ class CacheManager {
     requests.erase(it);
     return OK;
   }
-  int first_needed_page(int g, int start) const {    // lowest page that rows from position `start` on still read
+  int first_needed_page(int g, int start) const {    // lowest page of the window that rows from position `start` on read
     const int w = windows[g];
     if (w <= 0) return 0;
     return std::max(0, start + 1 - w) / page_size;
+  }
+  int kept_pages(int g) const {                      // pages that hold a kept first position: never given back
+    return windows[g] > 0 ? (std::max(0, keeps[g]) + page_size - 1) / page_size : 0;
   }
   void pages_needed(const RequestCache& rc, int start, int end, int* out) const {
     for (size_t g = 0; g < pools.size(); ++g) {
@@ -226,7 +233,7 @@ class CacheManager {
       const int fresh = std::max(0, total - (int)table.size());
       const int first = std::min(first_needed_page((int)g, start), (int)table.size());
       int back = 0;
-      for (int i = 0; i < first; ++i)
+      for (int i = kept_pages((int)g); i < first; ++i)
         if (table[i] >= 0 && pools[g].ref_count[table[i]] == 1) ++back;
       out[g] = fresh - back;
     }
@@ -249,7 +256,7 @@ class CacheManager {
     for (size_t g = 0; g < pools.size(); ++g) {
       auto& table = rc->tables[g];
       const int first = std::min(first_needed_page((int)g, start), (int)table.size());
-      for (int i = 0; i < first; ++i)
+      for (int i = kept_pages((int)g); i < first; ++i)
         if (table[i] >= 0) {
           int r = pools[g].release(table[i]);
           if (r) return r;
@@ -573,8 +580,9 @@ NVH_API int nvh_pool_check(void* p, const int* held) {
 
 // ---- the cache manager
 NVH_API void* nvh_manager_create(const int* windows, const int* num_pages, int groups, int page_size, int max_requests,
-                                 int prefix_caching, int has_state) {
-  return new CacheManager(windows, num_pages, groups, page_size, max_requests, prefix_caching != 0, has_state != 0);
+                                 int prefix_caching, int has_state, const int* keep_first) {
+  return new CacheManager(windows, num_pages, groups, page_size, max_requests, prefix_caching != 0, has_state != 0,
+                          keep_first);
 }
 NVH_API void nvh_manager_destroy(void* m) { delete (CacheManager*)m; }
 NVH_API void* nvh_manager_pool(void* m, int g) { return &((CacheManager*)m)->pools[g]; }

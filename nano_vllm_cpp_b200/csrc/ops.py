@@ -253,26 +253,28 @@ def random_fill(out, key: int, mean: float, std: float) -> None:
                                 mean, std, _stream()), "random_fill")
 
 
-def embedding(ids, table, out, err: ErrorFlag, feed=None, copies: int = 1) -> None:
+def embedding(ids, table, out, err: ErrorFlag, feed=None, copies: int = 1, scale: float = 1.0) -> None:
     """``feed``: int32 tokens that negative ids point into (id ``-(r + 1)`` reads ``feed[r]``).  ``copies``: a row of
-    ``out`` [T, copies * H] holds the token's row that many times, side by side."""
+    ``out`` [T, copies * H] holds the token's row that many times, side by side.  ``scale`` multiplies the row."""
     _cuda_contig(ids, table, out, feed)
     _i32(ids, feed)
     T, (V, H) = ids.numel(), table.shape
     _need(out.dtype == torch.float32 and out.shape == (T, copies * H), "embedding: out must be float32 [T, copies * H]")
     _check(lib().nv_embedding(_p(ids), _p(feed), _p(table), dt(table), _p(out), T, H, V, copies,
-                              _p(err.t), _stream()), "embedding")
+                              float(scale), _p(err.t), _stream()), "embedding")
 
 
-def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None) -> None:
-    """x (+= branch); out = rmsnorm(x) * w; optional float32 copy of out.
+def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None, branch2=None) -> None:
+    """x (+= branch (+ branch2)); out = rmsnorm(x) * w; optional float32 copy of out.
 
     ``mix`` = (rows, index, weight, dense, gate_logit) gives the branch as a sum that has not been taken yet:
     ``sigmoid(gate_logit[t]) * dense[t] + sum_r weight[t, r] * rows[index[t, r]]`` (dense and gate_logit may be
     None); it is summed inside the kernel instead of by ``moe_combine`` first."""
-    _cuda_contig(x, branch, w, out, out32)
+    _cuda_contig(x, branch, branch2, w, out, out32)
     T, H = x.shape
     _need(x.dtype == torch.float32, "add_rmsnorm: the residual stream is float32")
+    _need(branch2 is None or (branch is not None and branch2.dtype == torch.float32 and branch2.shape == x.shape),
+          "add_rmsnorm: a second branch comes with a first and is float32 and shaped like x")
     _need(branch is None or (branch.dtype == torch.float32 and branch.shape == x.shape),
           "add_rmsnorm: branch must be float32 and shaped like x")
     _need(w.numel() == H and out.shape == x.shape, "add_rmsnorm: shape mismatch")
@@ -293,9 +295,9 @@ def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None) -> None:
             _need(gate.dtype == torch.float32, "add_rmsnorm: gate logits are float32")
             gate_ld = gate.stride(0) if gate.dim() >= 1 else 1
     if H % 4 == 0:
-        for t_ in (x, branch, out, out32, rows, dense):
+        for t_ in (x, branch, branch2, out, out32, rows, dense):
             _need(t_ is None or t_.data_ptr() % 16 == 0, "add_rmsnorm: rows must start on 16-byte boundaries")
-    _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(w), dt(w), eps, _p(out), dt(out),
+    _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(branch2), _p(w), dt(w), eps, _p(out), dt(out),
                                 _p(out32), T, H, _p(rows), _p(index), _p(weight), R, _p(dense),
                                 _p(gate), gate_ld, _stream()), "add_rmsnorm")
 
@@ -744,7 +746,7 @@ def sample_nucleus(logits, params, recent, recent_off, out) -> None:
 
 
 # ----------------------------------------------------------------------------- state mixers and their layer pieces
-ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "xielu": 3}
 
 
 def _f32(*ts) -> None:
@@ -777,12 +779,13 @@ def branch_norm_add(x, branches, weight, eps: float, out=None, *, branch_weights
                                     (dt(out) if out is not None else 0), T, H, _stream()), "branch_norm_add")
 
 
-def activation(src, out, kind: str) -> None:
-    """``out = act(src)`` elementwise; ``kind``: gelu_erf, gelu_tanh or silu."""
+def activation(src, out, kind: str, params=(0.0, 0.0)) -> None:
+    """``out = act(src)`` elementwise; ``kind``: gelu_erf, gelu_tanh, silu, or xielu with ``params`` = (a, b), both
+    positive: ``a z^2 + z / 2`` for z > 0 and ``b (e^z - 1 - z) + z / 2`` for z <= 0."""
     _cuda_contig(src, out)
     _need(src.shape == out.shape and kind in ACTIVATIONS, "activation: shapes or kind")
-    _check(lib().nv_activation(_p(src), dt(src), _p(out), dt(out), src.numel(), ACTIVATIONS[kind], _stream()),
-           "activation")
+    _check(lib().nv_activation(_p(src), dt(src), _p(out), dt(out), src.numel(), ACTIVATIONS[kind], float(params[0]),
+                               float(params[1]), _stream()), "activation")
 
 
 def token_gate(gate, ids, table, col0: int, out, err: ErrorFlag, feed=None) -> None:
@@ -835,6 +838,12 @@ def col_scan_usable(dk: int, dv: int) -> bool:
     return bool(lib().nv_col_scan_usable(dk, dv))
 
 
+def channel_scan_usable(dk: int, dv: int) -> bool:
+    """Whether the fast form of the delta rule with channel decays takes these sizes (else the plain scan runs)."""
+    fn = getattr(lib(), "nv_channel_scan_usable", None)
+    return bool(fn(dk, dv)) if fn is not None else False
+
+
 def mlstm_scan(proj, cols: dict, batch, S, n, m, H: int, dk: int, dv: int, cap: float, eps: float, norm_w, out,
                *, den_eps: float = 1e-6, columns: bool = True) -> None:
     """The matrix memory with exponential gating, row by row per entry, from and to the entries' states.
@@ -862,13 +871,43 @@ def mlstm_scan(proj, cols: dict, batch, S, n, m, H: int, dk: int, dv: int, cap: 
 
 
 def gated_delta_scan(qkv, cols: dict, G: int, proj, pcols: dict, A_log, dt_bias, batch, S, H: int, dk: int, dv: int,
-                     eps: float, norm_w, out, *, columns: bool = True) -> None:
+                     eps: float, norm_w, out, *, columns: bool = True, channel_decay=None, gate_src=None,
+                     gate: str = "silu") -> None:
     """The gated delta rule, row by row per entry.  ``qkv`` float32 [T, C]: q, k, v after convolution and unit norm
     at ``cols`` (q, k, v); ``proj``: output gate, beta and decay pre-activations at ``pcols`` (g, b, a).
-    ``columns`` as in ``mlstm_scan``."""
+    ``columns`` as in ``mlstm_scan``.  ``channel_decay`` (float32 [T, >= a + H * dk]): the decay has one
+    pre-activation per head and key channel, at column ``pcols['a']`` of that matrix, and ``dt_bias`` is [H * dk].
+    ``gate_src``: the matrix that holds the output gate's pre-activations at ``pcols['g']`` where it is not ``proj``;
+    ``gate``: silu or sigmoid."""
     _cuda_contig(qkv, A_log, dt_bias, norm_w, out)
     _f32(qkv, A_log, dt_bias, norm_w)
     _need(proj.stride(-1) == 1 and norm_w.numel() == dv and out.shape == (qkv.shape[0], H * dv), "gated_delta_scan: shapes")
+    _need(gate in ("silu", "sigmoid"), "gated_delta_scan: the output gate is silu or sigmoid")
+    if channel_decay is not None or gate_src is not None or gate != "silu":
+        dec = channel_decay
+        if dec is not None:
+            _f32(dec)
+            _need(dec.stride(-1) == 1 and dec.shape[0] == qkv.shape[0] and dt_bias.numel() == H * dk
+                  and dec.shape[1] >= pcols["a"] + H * dk, "gated_delta_scan: channel decays")
+        gs = gate_src if gate_src is not None else proj
+        _need(gs.stride(-1) == 1 and gs.shape[0] == qkv.shape[0], "gated_delta_scan: gate rows")
+        if columns and col_scan_usable(dk, dv) and dec is not None and channel_scan_usable(dk, dv):
+            T = qkv.shape[0]
+            _check(lib().nv_channel_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj),
+                                               dt(proj), proj.stride(0), pcols["b"], _p(dec), dec.stride(0), pcols["a"],
+                                               _p(gs), dt(gs), gs.stride(0), pcols["g"], (1 if gate == "sigmoid" else 0),
+                                               _p(A_log), _p(dt_bias), _p(batch.cu_rows), _p(batch.entry_slot), _p(S),
+                                               _slot_stride(S), H, dk, dv, eps, _p(norm_w), _p(out), dt(out), batch.S,
+                                               T, _stream()), "channel_delta_scan")
+            return
+        _check(lib().nv_gated_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj), dt(proj),
+                                         proj.stride(0), pcols["g"], pcols["b"], (0 if dec is not None else pcols["a"]),
+                                         _p(A_log), _p(dt_bias), _p(batch.cu_rows), _p(batch.entry_slot), _p(S),
+                                         _slot_stride(S), H, dk, dv, eps, _p(norm_w), _p(out), dt(out), batch.S,
+                                         _p(dec), (dec.stride(0) if dec is not None else 0), pcols["a"], _p(gs), dt(gs),
+                                         gs.stride(0), (1 if dec is not None else 0), (1 if gate == "sigmoid" else 0),
+                                         _stream()), "gated_delta_scan")
+        return
     if columns and col_scan_usable(dk, dv):
         T = qkv.shape[0]
         raw = torch.empty((T, H, dv), dtype=torch.float32, device=qkv.device)
@@ -882,44 +921,115 @@ def gated_delta_scan(qkv, cols: dict, G: int, proj, pcols: dict, A_log, dt_bias,
     _check(lib().nv_gated_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj), dt(proj),
                                      proj.stride(0), pcols["g"], pcols["b"], pcols["a"], _p(A_log), _p(dt_bias),
                                      _p(batch.cu_rows), _p(batch.entry_slot), _p(S), _slot_stride(S), H, dk, dv, eps,
-                                     _p(norm_w), _p(out), dt(out), batch.S, _stream()), "gated_delta_scan")
+                                     _p(norm_w), _p(out), dt(out), batch.S, None, 0, 0, None, 0, 0, 0, 0, _stream()),
+           "gated_delta_scan")
 
 
 def qk_prepare_store(src, q0: int, k0: int, v0: int, positions, row_entry, block_table, q_weight, k_weight, eps: float,
                      inv_freq, rot_dim: int, interleaved: bool, amplitude: float, q_out, k_cache, v_cache,
-                     Hq: int, Hkv: int, D: int, Dv: int, write_kv: bool, err: ErrorFlag) -> None:
+                     Hq: int, Hkv: int, D: int, Dv: int, write_kv: bool, err: ErrorFlag, *, v_inv_freq=None,
+                     v_rot_dim: int = 0) -> None:
     """Per row: q and k heads RMS-normed over D (weights may be None), their first ``rot_dim`` elements turned in
-    pairs by the row's position, q to ``q_out`` [T, Hq * D], k and v to the row's place in their pages."""
-    _cuda_contig(positions, row_entry, block_table, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache)
+    pairs by the row's position, q to ``q_out`` [T, Hq * D], k and v to the row's place in their pages.
+    ``Hq`` may be 0 (``q_out`` None: only keys and values are written) and ``v_cache`` None (only keys).
+    ``v_rot_dim`` > 0: the first so many elements of every value head are turned too, in pairs
+    ``(i, i + v_rot_dim / 2)`` by ``position * v_inv_freq[i]``, before they are stored."""
+    _cuda_contig(positions, row_entry, block_table, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache, v_inv_freq)
     _i32(positions, row_entry, block_table)
-    _f32(q_weight, k_weight, inv_freq)
+    _f32(q_weight, k_weight, inv_freq, v_inv_freq)
     T = src.shape[0]
     page = k_cache.shape[2]
-    QP, KP, VP = q_out.shape[1] // Hq, k_cache.shape[3], v_cache.shape[3]      # a head's elements, padded with zeros
-    _need(src.stride(-1) == 1 and q_out.shape == (T, Hq * QP) and QP >= D, "qk_prepare_store: shapes")
-    _need(k_cache.shape[1:3] == (Hkv, page) and v_cache.shape[1:3] == (Hkv, page) and KP >= D and VP >= Dv
-          and k_cache.dtype == v_cache.dtype, "qk_prepare_store: cache shapes")
+    QP = q_out.shape[1] // Hq if Hq else D
+    KP, VP = k_cache.shape[3], (v_cache.shape[3] if v_cache is not None else Dv)   # a head's elements, padded with zeros
+    _need(src.stride(-1) == 1 and (Hq == 0 or q_out.shape == (T, Hq * QP)) and QP >= D, "qk_prepare_store: shapes")
+    _need(k_cache.shape[1:3] == (Hkv, page) and KP >= D and VP >= Dv, "qk_prepare_store: cache shapes")
+    _need(v_cache is None or (v_cache.shape[1:3] == (Hkv, page) and k_cache.dtype == v_cache.dtype),
+          "qk_prepare_store: cache shapes")
     _need(rot_dim == 0 or inv_freq.numel() >= rot_dim // 2, "qk_prepare_store: inv_freq")
+    _need(v_rot_dim == 0 or (v_inv_freq is not None and v_inv_freq.numel() >= v_rot_dim // 2), "qk_prepare_store: v_inv_freq")
     _check(lib().nv_qk_prepare_store(_p(src), dt(src), src.stride(0), q0, k0, v0, _p(positions), _p(row_entry),
                                      _p(block_table), block_table.shape[1], _p(q_weight), _p(k_weight), eps,
-                                     _p(inv_freq), rot_dim, (1 if interleaved else 0), amplitude, _p(q_out), dt(q_out),
+                                     _p(inv_freq), rot_dim, (1 if interleaved else 0), amplitude, _p(q_out),
+                                     (dt(q_out) if q_out is not None else 0),
                                      _p(k_cache), _p(v_cache), dt(k_cache), Hq, Hkv, D, Dv, page,
-                                     (1 if write_kv else 0), _p(err.t), T, QP, KP, VP, _stream()), "qk_prepare_store")
+                                     (1 if write_kv else 0), _p(err.t), T, QP, KP, VP, _p(v_inv_freq), v_rot_dim,
+                                     _stream()), "qk_prepare_store")
 
 
 def paged_attention_general(q, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
-                            Hq: int, Hkv: int, D: int, Dv: int, sink_score=None) -> None:
+                            Hq: int, Hkv: int, D: int, Dv: int, sink_score=None, *, sinks=None, keep_first: int = 0,
+                            key_span: int = 1, value_heads: int | None = None) -> None:
     """Causal softmax attention of every row over its request's paged keys; values may be wider or narrower than
-    keys; ``sink_score``: a further key with that score and no value in every softmax (None: none)."""
-    _cuda_contig(q, k_cache, v_cache, block_table, row_entry, positions, out)
+    keys; ``sink_score``: a further key with that score and no value in every softmax (None: none), ``sinks``
+    (float32 [Hq]): one such score per head; ``keep_first``: with a window, the sequence's first so many positions
+    stay visible; ``key_span`` = Hkv: a query row holds Hkv * D elements per head and a score is the sum of its
+    parts' products with all kv heads' keys (see ``mix_query_heads``); ``v_cache`` None: the values are read where
+    the keys are; ``value_heads``: kv heads of the values where that is not ``Hkv``."""
+    if v_cache is None:
+        v_cache = k_cache
+    Hv = Hkv if value_heads is None else value_heads
+    _cuda_contig(q, k_cache, v_cache, block_table, row_entry, positions, out, sinks)
     _i32(block_table, row_entry, positions)
+    _f32(sinks)
     T = q.shape[0]
-    _need(q.shape == (T, Hq * D) and out.shape == (T, Hq * Dv), "attention: shapes")
+    _need(q.shape == (T, Hq * key_span * D) and out.shape == (T, Hq * Dv), "attention: shapes")
+    _need(k_cache.shape[1] == Hkv and k_cache.shape[3] == D and v_cache.shape[1] == Hv and v_cache.shape[3] == Dv
+          and k_cache.dtype == v_cache.dtype, "attention: cache shapes")
+    _need(sinks is None or sinks.numel() == Hq, "attention: one sink per query head")
     _check(lib().nv_paged_attention_general(_p(q), dt(q), _p(k_cache), _p(v_cache), dt(k_cache), _p(block_table),
                                             block_table.shape[1], _p(row_entry), _p(positions), scale, window,
-                                            (0 if sink_score is None else 1), float(sink_score or 0.0), _p(out),
-                                            dt(out), T, Hq, Hkv, D, Dv, k_cache.shape[2], _stream()),
+                                            keep_first, (0 if sink_score is None else 1), float(sink_score or 0.0),
+                                            _p(sinks), _p(out), dt(out), T, Hq, Hkv, Hv, D, Dv, key_span,
+                                            k_cache.shape[2], _stream()),
            "paged_attention_general")
+
+
+def mix_query_heads(q, mix, out, H: int, G: int, D: int) -> None:
+    """``out[t, h, c * D + d] = sum over the heads g of kv head c of mix[h, g] * q[t, g, d]``: the query rows of
+    an attention whose scores are mixed across heads before the softmax (``q`` float32 [T, H * D], ``mix`` float32
+    [H, H], ``out`` [T, H * G * D])."""
+    _cuda_contig(q, mix, out)
+    _f32(q, mix)
+    T = q.shape[0]
+    _need(q.shape == (T, H * D) and mix.shape == (H, H) and out.shape == (T, H * G * D), "mix_query_heads: shapes")
+    _check(lib().nv_mix_query_heads(_p(q), _p(mix), _p(out), dt(out), T, H, G, D, _stream()), "mix_query_heads")
+
+
+def rotate_heads(x, positions, inv_freq, rot_dim: int, sign: float, out, H: int, D: int) -> None:
+    """The first ``rot_dim`` elements of every head of ``x`` [T, H * D] turned in pairs ``(i, i + rot_dim / 2)`` by
+    ``sign * position * inv_freq[i]``, written to ``out`` (another tensor, any of the two dtypes)."""
+    _cuda_contig(x, positions, inv_freq, out)
+    _i32(positions)
+    _f32(inv_freq)
+    T = x.shape[0]
+    _need(x.shape == (T, H * D) and out.shape == x.shape and inv_freq.numel() >= rot_dim // 2
+          and x.data_ptr() != out.data_ptr(), "rotate_heads: shapes")
+    _check(lib().nv_rotate_heads(_p(x), dt(x), _p(positions), _p(inv_freq), rot_dim, float(sign), _p(out), dt(out),
+                                 T, H, D, _stream()), "rotate_heads")
+
+
+def cols_rmsnorm(src, col0: int, n: int, w, eps: float, out) -> None:
+    """``out = rms(src[:, col0:col0 + n]) * w`` for float32 rows, the norm over the ``n`` columns."""
+    _cuda_contig(w, out)
+    _f32(src, w)
+    T = src.shape[0]
+    _need(src.stride(-1) == 1 and src.shape[1] >= col0 + n and out.shape == (T, n) and w.numel() == n,
+          "cols_rmsnorm: shapes")
+    _check(lib().nv_cols_rmsnorm(_p(src), src.stride(0), col0, n, _p(w), eps, _p(out), dt(out), T, _stream()),
+           "cols_rmsnorm")
+
+
+def head_project(x, w, out, H: int, K: int, N: int, gate=None, gate_col: int = 0) -> None:
+    """``out[t, h, :] = x[t, h, :] @ w[h]`` for float32 ``x`` [T, H * K] and ``w`` [H, K, N]; with ``gate`` (float32
+    rows, column ``gate_col + h``) the head's output is multiplied by the sigmoid of its gate."""
+    _cuda_contig(x, w, out)
+    _f32(x, gate)
+    T = x.shape[0]
+    _need(x.shape == (T, H * K) and w.shape == (H, K, N) and out.shape == (T, H * N), "head_project: shapes")
+    _need(gate is None or (gate.stride(-1) == 1 and gate.shape[0] == T and gate.shape[1] >= gate_col + H),
+          "head_project: gate rows")
+    _check(lib().nv_head_project(_p(x), _p(w), dt(w), _p(gate), (gate.stride(0) if gate is not None else 0), gate_col,
+                                 _p(out), dt(out), T, H, K, N, _stream()), "head_project")
 
 
 # ----------------------------------------------------------------------------- fast products

@@ -17,7 +17,7 @@ namespace {
 // seen the tokens of the step before.
 __global__ void embedding_kernel(const int* __restrict__ ids, const void* __restrict__ table, int dt,
                                  float* __restrict__ out, int H, int V, int* __restrict__ err,
-                                 const int* __restrict__ feed, int copies) {
+                                 const int* __restrict__ feed, int copies, float scale) {
   grid_dep_wait();
   grid_dep_launch();
   int t = blockIdx.x;
@@ -30,7 +30,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const void* __rest
   // `copies` > 1: a row of `out` holds that many copies of the table's row side by side (a model that keeps
   // several copies of its residual stream starts them all from the embedding)
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = ld_dt(table, dt, (size_t)id * H + i);
+    const float v = ld_dt(table, dt, (size_t)id * H + i) * scale;     // (scale 1 changes nothing)
     for (int c = 0; c < copies; ++c) out[((size_t)t * copies + c) * H + i] = v;
   }
 }
@@ -50,6 +50,7 @@ constexpr int NORM_THREADS = 256, NORM_CACHE = 4, NORM_MAX_R = 64;
 struct NormArgs {
   float* x;
   const float* branch;
+  const float* branch2;     // a second matrix added with the first (two sublayers that read the same rows), or null
   const void* w;
   void* out;
   float* out32;
@@ -113,6 +114,11 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
     Chunk<VEC> v = ld_chunk<VEC>(a.x + base + (size_t)c * VEC);
     if (a.branch) {
       Chunk<VEC> b = ld_chunk<VEC>(a.branch + base + (size_t)c * VEC);
+      if (a.branch2) {          // x + (b + b2): the branches are summed first
+        Chunk<VEC> b2 = ld_chunk<VEC>(a.branch2 + base + (size_t)c * VEC);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) b.v[j] += b2.v[j];
+      }
 #pragma unroll
       for (int j = 0; j < VEC; ++j) v.v[j] += b.v[j];
     } else if (a.R > 0 || a.dense) {
@@ -559,25 +565,26 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 NV_API const char* nv_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 
 NV_API int nv_embedding(const int* ids, const int* feed, const void* table, int table_dt, float* out, int T, int H, int V,
-                        int copies, int* err, cudaStream_t s) {
+                        int copies, float scale, int* err, cudaStream_t s) {
   if (!dt_ok(table_dt)) return NV_ERR_BAD_DTYPE;
   if (copies < 1) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   NV_RETURN_IF(launch_dep(embedding_kernel, dim3(T), dim3(256), 0, s, ids, table, table_dt, out, H, V, err, feed,
-                          copies));
+                          copies, scale));
   NV_RETURN_LAST();
 }
 
-NV_API int nv_add_rmsnorm(float* x, const float* branch, const void* w, int w_dt, float eps, void* out,
+NV_API int nv_add_rmsnorm(float* x, const float* branch, const float* branch2, const void* w, int w_dt, float eps, void* out,
                           int out_dt, float* out32, int T, int H, const float* rows, const int* index,
                           const float* weight, int R, const float* dense, const float* gate_logit,
                           long long gate_ld, cudaStream_t s) {
   if (!dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (R < 0 || R > NORM_MAX_R || (R > 0 && (!rows || !index || !weight))) return NV_ERR_BAD_SIZE;
   if (branch && (R > 0 || dense)) return NV_ERR_BAD_SIZE;   // one form of the branch at a time
+  if (branch2 && !branch) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   NormArgs a;
-  a.x = x; a.branch = branch; a.w = w; a.out = out; a.out32 = out32; a.rows = rows; a.index = index;
+  a.x = x; a.branch = branch; a.branch2 = branch2; a.w = w; a.out = out; a.out32 = out32; a.rows = rows; a.index = index;
   a.weight = weight; a.dense = dense; a.gate_logit = gate_logit; a.gate_ld = gate_ld; a.eps = eps;
   a.w_dt = w_dt; a.out_dt = out_dt; a.H = H; a.R = R;
   if (H % 4 == 0) NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<4>, dim3(T), dim3(NORM_THREADS), 0, s, a));

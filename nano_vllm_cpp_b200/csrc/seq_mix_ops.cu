@@ -89,25 +89,27 @@ __global__ void __launch_bounds__(SM_THREADS) branch_norm_add_kernel(BranchArgs 
 }
 
 // ------------------------------------------------------------------ activation over a matrix
-__device__ __forceinline__ float act_of(int kind, float z) {
+// kind 3, xIELU with the two positive numbers (p0, p1): z > 0: p0 z^2 + z / 2; z <= 0: p1 (e^z - 1 - z) + z / 2
+__device__ __forceinline__ float act_of(int kind, float z, float p0 = 0.f, float p1 = 0.f) {
+  if (kind == 3) return z > 0.f ? fmaf(p0 * z, z, 0.5f * z) : fmaf(p1, expm1f(z) - z, 0.5f * z);
   return kind == 0 ? gelu_erf_(z) : (kind == 1 ? gelu_tanh_(z) : siluf_(z));
 }
 
 __global__ void activation_kernel(const void* __restrict__ in, int in_dt, void* __restrict__ out, int out_dt,
-                                  long long n, int kind) {
+                                  long long n, int kind, float p0, float p1) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  st_dt(out, out_dt, i, act_of(kind, ld_dt(in, in_dt, i)));
+  st_dt(out, out_dt, i, act_of(kind, ld_dt(in, in_dt, i), p0, p1));
 }
 
 // float32 in, bfloat16 out, four values per thread (16 bytes in, 8 out): what a bfloat16 prompt's MLP runs
 __global__ void activation_f32_bf16_x4_kernel(const float4* __restrict__ in, uint2* __restrict__ out, long long n4,
-                                              int kind) {
+                                              int kind, float p0, float p1) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
   const float4 z = in[i];
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(act_of(kind, z.x), act_of(kind, z.y));
-  const __nv_bfloat162 hi = __floats2bfloat162_rn(act_of(kind, z.z), act_of(kind, z.w));
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(act_of(kind, z.x, p0, p1), act_of(kind, z.y, p0, p1));
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(act_of(kind, z.z, p0, p1), act_of(kind, z.w, p0, p1));
   uint2 o;
   o.x = *reinterpret_cast<const uint32_t*>(&lo);
   o.y = *reinterpret_cast<const uint32_t*>(&hi);
@@ -310,7 +312,17 @@ struct DeltaArgs {
   long long ld;
   int g0, b0, a0;
   const float* A_log;       // [H]
-  const float* dt_bias;     // [H]
+  const float* dt_bias;     // [H], or [H * dk] with a decay per key channel
+  // decay_mode 1: one decay per head and key channel, g[r] = exp(-exp(A_log[h]) softplus(dec[t, dec0 + h dk + r] +
+  // dt_bias[h dk + r])), acting on row r of the head's matrix.  gate_mode 1: the output gate is a sigmoid (0: silu).
+  // The output gate's pre-activations are read from gsrc (column g0), which may be another matrix than proj.
+  const float* dec;         // [T, dec_ld] float32
+  long long dec_ld;
+  int dec0;
+  const void* gsrc;
+  int gsrc_dt;
+  long long gsrc_ld;
+  int decay_mode, gate_mode;
 };
 
 __global__ void __launch_bounds__(SM_THREADS) gated_delta_scan_kernel(DeltaArgs a) {
@@ -326,24 +338,28 @@ __global__ void __launch_bounds__(SM_THREADS) gated_delta_scan_kernel(DeltaArgs 
   float* u = partq + RS * dv;        // dv
   float* o = u + dv;                 // dv
   float* sc = o + dv;                // 8 scalars
+  float* gv = sc + 8;                // dk: the key channels' decays (decay_mode 1)
   const int e = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int gh = h / (H / a.G);
+  const bool chan = a.decay_mode == 1;
   const int row0 = a.c.cu_rows[e], row1 = a.c.cu_rows[e + 1];
   float* Sg = a.c.S + (size_t)a.c.entry_slot[e] * a.c.S_stride + (size_t)h * dk * dv;
   for (int i = tid; i < dk * dv; i += SM_THREADS) S[i] = Sg[i];
   const int c = tid % dv, rs = tid / dv;
   const bool owner = tid < RS * dv;
-  const float rate = expf(a.A_log[h]), dtb = a.dt_bias[h];
+  const float rate = expf(a.A_log[h]), dtb = chan ? 0.f : a.dt_bias[h];
   __syncthreads();
   for (int t = row0; t < row1; ++t) {
     const float* x = a.qkv + (size_t)t * a.C;
     for (int i = tid; i < dk; i += SM_THREADS) {
       q[i] = x[a.q0 + gh * dk + i];
       k[i] = x[a.k0 + gh * dk + i];
+      if (chan)
+        gv[i] = expf(-rate * softplusf_(a.dec[(size_t)t * a.dec_ld + a.dec0 + h * dk + i] + a.dt_bias[h * dk + i]));
     }
     for (int i = tid; i < dv; i += SM_THREADS) v[i] = x[a.v0 + h * dv + i];
     const float beta = sigmoidf_(ld_dt(a.proj, a.proj_dt, (size_t)t * a.ld + a.b0 + h));
-    const float g = expf(-rate * softplusf_(ld_dt(a.proj, a.proj_dt, (size_t)t * a.ld + a.a0 + h) + dtb));
+    const float g = chan ? 1.f : expf(-rate * softplusf_(ld_dt(a.proj, a.proj_dt, (size_t)t * a.ld + a.a0 + h) + dtb));
     __syncthreads();
     if (tid < 32) {
       float acc = 0.f;
@@ -353,10 +369,18 @@ __global__ void __launch_bounds__(SM_THREADS) gated_delta_scan_kernel(DeltaArgs 
     }
     if (owner) {
       float ak = 0.f, aq = 0.f;
-      for (int r = rs; r < dk; r += RS) {
-        const float s = S[r * dv + c];
-        ak = fmaf(s, k[r], ak);
-        aq = fmaf(s, q[r], aq);
+      if (chan) {
+        for (int r = rs; r < dk; r += RS) {
+          const float s = S[r * dv + c] * gv[r];      // the decayed row, as the update below leaves it
+          ak = fmaf(s, k[r], ak);
+          aq = fmaf(s, q[r], aq);
+        }
+      } else {
+        for (int r = rs; r < dk; r += RS) {
+          const float s = S[r * dv + c];
+          ak = fmaf(s, k[r], ak);
+          aq = fmaf(s, q[r], aq);
+        }
       }
       partk[rs * dv + c] = ak;
       partq[rs * dv + c] = aq;
@@ -372,7 +396,10 @@ __global__ void __launch_bounds__(SM_THREADS) gated_delta_scan_kernel(DeltaArgs 
     __syncthreads();
     if (owner) {
       const float uu = u[c];
-      for (int r = rs; r < dk; r += RS) S[r * dv + c] = g * S[r * dv + c] + k[r] * uu;
+      if (chan)
+        for (int r = rs; r < dk; r += RS) S[r * dv + c] = fmaf(k[r], uu, S[r * dv + c] * gv[r]);
+      else
+        for (int r = rs; r < dk; r += RS) S[r * dv + c] = g * S[r * dv + c] + k[r] * uu;
     }
     if (tid < 32) {
       float ss = 0.f;
@@ -382,7 +409,8 @@ __global__ void __launch_bounds__(SM_THREADS) gated_delta_scan_kernel(DeltaArgs 
     }
     __syncthreads();
     if (tid < dv) {
-      const float gate = siluf_(ld_dt(a.proj, a.proj_dt, (size_t)t * a.ld + a.g0 + h * dv + tid));
+      const float gz = ld_dt(a.gsrc, a.gsrc_dt, (size_t)t * a.gsrc_ld + a.g0 + h * dv + tid);
+      const float gate = a.gate_mode == 1 ? sigmoidf_(gz) : siluf_(gz);
       st_dt(a.c.out, a.c.out_dt, (size_t)t * H * dv + (size_t)h * dv + tid, o[tid] * sc[1] * a.c.norm_w[tid] * gate);
     }
   }
@@ -420,6 +448,8 @@ struct QkArgs {
   int Hq, Hkv, D, Dv, page, write_kv;
   int* err;
   int QP, KP, VP;           // elements per head in q_out, in the key pages and in the value pages (>= D, D, Dv; the rest is zero)
+  const float* v_inv_freq;  // values are turned too: the first v_rot_dim elements of every value head, in pairs
+  int v_rot_dim;            // (i, i + v_rot_dim / 2), by position * v_inv_freq[i]; 0: values are stored as projected
 };
 
 constexpr int QK_THREADS = 128;
@@ -474,47 +504,77 @@ __global__ void __launch_bounds__(QK_THREADS) qk_prepare_store_kernel(QkArgs a) 
     }
     __syncwarp();
   }
-  if (write_kv) {
+  if (write_kv && a.vc) {
+    const int vhalf = a.v_rot_dim / 2;
     for (int i = threadIdx.x; i < a.Hkv * a.VP; i += QK_THREADS) {
       const int hv = i / a.VP, d = i % a.VP;
       const size_t dst = (((size_t)blk * a.Hkv + hv) * a.page + slot) * a.VP + d;
-      st_dt(a.vc, a.cache_dt, dst, d < a.Dv ? ld_dt(a.in, a.in_dt, (size_t)t * a.ld + a.v0 + hv * a.Dv + d) : 0.f);
+      const size_t src = (size_t)t * a.ld + a.v0 + hv * a.Dv;
+      float x = d < a.Dv ? ld_dt(a.in, a.in_dt, src + d) : 0.f;
+      if (d < a.v_rot_dim) {
+        const int pr = d < vhalf ? d : d - vhalf;
+        const float ang = (float)pos * a.v_inv_freq[pr];
+        const float cs = cosf(ang), sn = sinf(ang);
+        const float other = ld_dt(a.in, a.in_dt, src + (d < vhalf ? d + vhalf : d - vhalf));
+        x = d < vhalf ? x * cs - other * sn : x * cs + other * sn;
+      }
+      st_dt(a.vc, a.cache_dt, dst, x);
     }
   }
 }
 
 // ------------------------------------------------------------------ paged softmax attention, general sizes
-// One block per (row, query head).  Keys of D elements, values of Dv; with `has_sink` the softmax's denominator
-// also holds exp(sink_score): a key with that score and no value.  Chunks of ATTG_THREADS keys, running maximum.
+// One block per (row, query head).  Keys of D elements, values of Dv.  A softmax may hold a *sink*, a score without
+// a key or a value that counts once in the denominator: one score for all heads (`has_sink`) or a learned one per
+// head (`sinks`).  `keep_first` > 0 with a window: the first so many positions of the sequence stay visible after
+// the window has passed them.  `key_span` = KS > 1: a query row holds KS * D elements per head and its score with
+// position j is the sum of its KS parts' products with the keys of kv heads 0 .. KS - 1 at j (scores that are mixed
+// across heads are linear in the queries, so the mixing is done once per row on the queries); values are read from
+// the head's own kv head as always.  Chunks of ATTG_THREADS keys, running maximum.
 constexpr int ATTG_THREADS = 128;
+constexpr int ATTG_NV = 4;           // output elements per thread: values up to ATTG_NV * ATTG_THREADS wide
 
 __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
     const void* __restrict__ q, int q_dt, const void* __restrict__ kc, const void* __restrict__ vc, int cache_dt,
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_entry,
-    const int* __restrict__ positions, float scale, int window, int has_sink, float sink_score,
-    void* __restrict__ out, int out_dt, int Hq, int Hkv, int D, int Dv, int page) {
-  __shared__ float qs[256];
+    const int* __restrict__ positions, float scale, int window, int keep_first, int has_sink, float sink_score,
+    const float* __restrict__ sinks, void* __restrict__ out, int out_dt, int Hq, int Hkv, int Hv, int D, int Dv,
+    int KS, int page) {
+  extern __shared__ float qs[];      // KS * D
   __shared__ float p[ATTG_THREADS];
   __shared__ int pslot[ATTG_THREADS];
   __shared__ float red[ATTG_THREADS / 32];
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int kvh = h / (Hq / Hkv);
+  const int kvh = KS > 1 ? 0 : h / (Hq / Hkv);     // first key head of the score
+  const int vh = h / (Hq / Hv);                    // the head's value head
   const int n = positions[t] + 1;
   const int lo = window > 0 ? max(0, n - window) : 0;
+  const int nkeep = min(keep_first, lo);           // kept positions that the window no longer covers
+  const int total = nkeep + (n - lo);
   const int* bt = block_table + (size_t)row_entry[t] * max_blocks;
-  for (int d = tid; d < D; d += ATTG_THREADS) qs[d] = ld_dt(q, q_dt, (size_t)t * Hq * D + (size_t)h * D + d);
+  const int QD = KS * D;
+  for (int d = tid; d < QD; d += ATTG_THREADS) qs[d] = ld_dt(q, q_dt, (size_t)t * Hq * QD + (size_t)h * QD + d);
   __syncthreads();
+  if (sinks) { has_sink = 1; sink_score = sinks[h]; }
   float m = has_sink ? sink_score : -1e30f, l = has_sink ? 1.f : 0.f;
-  float o0 = 0.f, o1 = 0.f;          // output elements tid and tid + ATTG_THREADS
-  for (int c0 = lo; c0 < n; c0 += ATTG_THREADS) {
-    const int j = c0 + tid;
+  float o[ATTG_NV];
+#pragma unroll
+  for (int u = 0; u < ATTG_NV; ++u) o[u] = 0.f;
+  for (int c0 = 0; c0 < total; c0 += ATTG_THREADS) {
+    const int i = c0 + tid;
     float s = -1e30f;
-    if (j < n) {
+    if (i < total) {
+      const int j = i < nkeep ? i : lo + (i - nkeep);
       const int blk = bt[j / page];
-      const size_t slot = ((size_t)blk * Hkv + kvh) * page + j % page;
-      pslot[tid] = (int)slot;
+      const size_t slot = (size_t)blk * page + j % page;       // [page][head][slot]: head added below
+      pslot[tid] = (int)(((size_t)blk * Hv + vh) * page + j % page);
       float acc = 0.f;
-      for (int d = 0; d < D; ++d) acc = fmaf(qs[d], ld_dt(kc, cache_dt, slot * D + d), acc);
+      for (int c = 0; c < KS; ++c) {
+        const size_t kb = ((size_t)blk * Hkv + kvh + c) * page + j % page;
+        const float* qq = qs + c * D;
+        for (int d = 0; d < D; ++d) acc = fmaf(qq[d], ld_dt(kc, cache_dt, kb * D + d), acc);
+      }
+      (void)slot;
       s = acc * scale;
     }
     // maximum over the chunk
@@ -523,32 +583,133 @@ __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
     if ((tid & 31) == 0) red[tid >> 5] = mx;
     __syncthreads();
     mx = red[0];
-    for (int i = 1; i < ATTG_THREADS / 32; ++i) mx = fmaxf(mx, red[i]);
+    for (int i2 = 1; i2 < ATTG_THREADS / 32; ++i2) mx = fmaxf(mx, red[i2]);
     const float m_new = fmaxf(m, mx);
-    const float ex = j < n ? expf(s - m_new) : 0.f;
+    const float ex = i < total ? expf(s - m_new) : 0.f;
     p[tid] = ex;
     float sum = warp_sum(ex);
     __syncthreads();
     if ((tid & 31) == 0) red[tid >> 5] = sum;
     __syncthreads();
     sum = 0.f;
-    for (int i = 0; i < ATTG_THREADS / 32; ++i) sum += red[i];
+    for (int i2 = 0; i2 < ATTG_THREADS / 32; ++i2) sum += red[i2];
     const float alpha = expf(m - m_new);
     l = l * alpha + sum;
     m = m_new;
-    const int cnt = min(ATTG_THREADS, n - c0);
-    o0 *= alpha;
-    o1 *= alpha;
-    if (tid < Dv)
-      for (int i = 0; i < cnt; ++i) o0 = fmaf(p[i], ld_dt(vc, cache_dt, (size_t)pslot[i] * Dv + tid), o0);
-    if (tid + ATTG_THREADS < Dv)
-      for (int i = 0; i < cnt; ++i) o1 = fmaf(p[i], ld_dt(vc, cache_dt, (size_t)pslot[i] * Dv + tid + ATTG_THREADS), o1);
+    const int cnt = min(ATTG_THREADS, total - c0);
+#pragma unroll
+    for (int u = 0; u < ATTG_NV; ++u) {
+      const int d = tid + u * ATTG_THREADS;
+      o[u] *= alpha;
+      if (d < Dv)
+        for (int i2 = 0; i2 < cnt; ++i2) o[u] = fmaf(p[i2], ld_dt(vc, cache_dt, (size_t)pslot[i2] * Dv + d), o[u]);
+    }
     __syncthreads();
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
   const size_t ob = (size_t)t * Hq * Dv + (size_t)h * Dv;
-  if (tid < Dv) st_dt(out, out_dt, ob + tid, o0 * inv);
-  if (tid + ATTG_THREADS < Dv) st_dt(out, out_dt, ob + tid + ATTG_THREADS, o1 * inv);
+#pragma unroll
+  for (int u = 0; u < ATTG_NV; ++u) {
+    const int d = tid + u * ATTG_THREADS;
+    if (d < Dv) st_dt(out, out_dt, ob + d, o[u] * inv);
+  }
+}
+
+// ------------------------------------------------------------------ queries mixed across heads
+// q [T, H, D] float32 -> out [T, H, G * D]: out[t, h, c D + d] = sum over the heads g of kv head c of
+// mix[h, g] * q[t, g, d].  With it, sum_g mix[h, g] (q_g . k_kv(g)) is one product of the mixed query row with the
+// kv heads' keys side by side.  One block per row.
+__global__ void __launch_bounds__(256) mix_query_heads_kernel(const float* __restrict__ q, const float* __restrict__ mix,
+                                                              void* __restrict__ out, int out_dt, int H, int G, int D) {
+  extern __shared__ float sm[];      // H * D query elements, then H * H weights
+  float* qs = sm;
+  float* w = sm + H * D;
+  const int t = blockIdx.x, rep = H / G;
+  for (int i = threadIdx.x; i < H * D; i += blockDim.x) qs[i] = q[(size_t)t * H * D + i];
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x) w[i] = mix[i];
+  __syncthreads();
+  const int n = H * G * D;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int h = i / (G * D), c = (i / D) % G, d = i % D;
+    float acc = 0.f;
+    for (int g = c * rep; g < (c + 1) * rep; ++g) acc = fmaf(w[h * H + g], qs[g * D + d], acc);
+    st_dt(out, out_dt, (size_t)t * n + i, acc);
+  }
+}
+
+// ------------------------------------------------------------------ rotation of whole heads
+// x [T, H, D] (in_dt) -> out (out_dt): the first rot_dim elements of every head turned in pairs (i, i + rot_dim / 2)
+// by sign * position * inv_freq[i].  sign -1 turns back what was turned by the same position.
+__global__ void rotate_heads_kernel(const void* __restrict__ x, int in_dt, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int rot_dim, float sign, void* __restrict__ out,
+                                    int out_dt, int H, int D, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int d = (int)(i % D);
+  const long long t = i / ((long long)H * D);
+  const int half = rot_dim / 2;
+  float v = ld_dt(x, in_dt, i);
+  if (d < rot_dim) {
+    const int pr = d < half ? d : d - half;
+    const float ang = sign * (float)positions[t] * inv_freq[pr];
+    const float cs = cosf(ang), sn = sinf(ang);
+    const float other = ld_dt(x, in_dt, d < half ? i + half : i - half);
+    v = d < half ? v * cs - other * sn : v * cs + other * sn;
+  }
+  st_dt(out, out_dt, i, v);
+}
+
+// ------------------------------------------------------------------ RMS norm of a run of columns
+// out[t, :] = rms(in[t, col0 .. col0 + n)) * w, the mean of squares taken over the n columns; one block per row.
+__global__ void __launch_bounds__(SM_THREADS) cols_rmsnorm_kernel(const float* __restrict__ in, long long ld, int col0,
+                                                                  int n, const float* __restrict__ w, float eps,
+                                                                  void* __restrict__ out, int out_dt) {
+  __shared__ float red[SM_THREADS / 32];
+  const int t = blockIdx.x;
+  const float* x = in + (size_t)t * ld + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += SM_THREADS) ss = fmaf(x[i], x[i], ss);
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += SM_THREADS) st_dt(out, out_dt, (size_t)t * n + i, x[i] * r * w[i]);
+}
+
+// ------------------------------------------------------------------ a small product per head
+// x [T, H, K] float32, w [H, K, N] (float32 or bfloat16) -> out [T, H, N] = x[t, h, :] w[h]; with `gate` the head's
+// output is multiplied by sigmoid(gate[t, gate0 + h]).  A block takes HP_ROWS rows of one head, so a weight is read
+// once for all of them; a thread owns output columns and sums over k in ascending order.
+constexpr int HP_ROWS = 8;
+constexpr int HP_THREADS = 128;
+
+__global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const float* __restrict__ x, const void* __restrict__ w,
+                                                                  int w_dt, const float* __restrict__ gate,
+                                                                  long long gate_ld, int gate0, void* __restrict__ out,
+                                                                  int out_dt, int T, int H, int K, int N) {
+  extern __shared__ float xs[];      // HP_ROWS * K
+  const int t0 = blockIdx.x * HP_ROWS, h = blockIdx.y;
+  const int rows = min(HP_ROWS, T - t0);
+  for (int i = threadIdx.x; i < HP_ROWS * K; i += HP_THREADS) {
+    const int r = i / K, k = i % K;
+    xs[i] = r < rows ? x[((size_t)(t0 + r) * H + h) * K + k] : 0.f;
+  }
+  __syncthreads();
+  float g[HP_ROWS];
+#pragma unroll
+  for (int r = 0; r < HP_ROWS; ++r)
+    g[r] = gate && r < rows ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + h]) : 1.f;
+  for (int n = threadIdx.x; n < N; n += HP_THREADS) {
+    float acc[HP_ROWS];
+#pragma unroll
+    for (int r = 0; r < HP_ROWS; ++r) acc[r] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const float wv = ld_dt(w, w_dt, ((size_t)h * K + k) * N + n);
+#pragma unroll
+      for (int r = 0; r < HP_ROWS; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < HP_ROWS; ++r)
+      if (r < rows) st_dt(out, out_dt, ((size_t)(t0 + r) * H + h) * N + n, acc[r] * g[r]);
+  }
 }
 
 // ------------------------------------------------------------------ the same memories, a column per thread
@@ -888,16 +1049,17 @@ NV_API int nv_branch_norm_add(float* x, const float* b0, const float* b1, const 
   NV_RETURN_LAST();
 }
 
-NV_API int nv_activation(const void* in, int in_dt, void* out, int out_dt, long long n, int kind, cudaStream_t s) {
+NV_API int nv_activation(const void* in, int in_dt, void* out, int out_dt, long long n, int kind, float p0, float p1,
+                         cudaStream_t s) {
   if (!dt_ok(in_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
-  if (kind < 0 || kind > 2) return NV_ERR_UNSUPPORTED;
+  if (kind < 0 || kind > 3) return NV_ERR_UNSUPPORTED;
   if (n == 0) return NV_OK;
   if (in_dt == NV_DT_F32 && out_dt == NV_DT_BF16 && n % 4 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 7) == 0) {
     const long long n4 = n / 4;
-    activation_f32_bf16_x4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>((const float4*)in, (uint2*)out, n4, kind);
+    activation_f32_bf16_x4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>((const float4*)in, (uint2*)out, n4, kind, p0, p1);
     NV_RETURN_LAST();
   }
-  activation_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(in, in_dt, out, out_dt, n, kind);
+  activation_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(in, in_dt, out, out_dt, n, kind, p0, p1);
   NV_RETURN_LAST();
 }
 
@@ -967,15 +1129,21 @@ NV_API int nv_gated_delta_scan(const float* qkv, int C, int q0, int k0, int v0, 
                                long long ld, int g0, int b0, int a0, const float* A_log, const float* dt_bias,
                                const int* cu_rows, const int* entry_slot, float* S, long long S_stride, int H, int dk,
                                int dv, float eps, const float* norm_w, void* out, int out_dt, int num_entries,
-                               cudaStream_t s) {
+                               const float* dec, long long dec_ld, int dec0, const void* gsrc, int gsrc_dt,
+                               long long gsrc_ld, int decay_mode, int gate_mode, cudaStream_t s) {
   if (!dt_ok(out_dt) || !dt_ok(proj_dt)) return NV_ERR_BAD_DTYPE;
   if (!nv_scan_usable(dk, dv, 2) || H <= 0 || G <= 0 || H % G) return NV_ERR_UNSUPPORTED;
+  if (decay_mode < 0 || decay_mode > 1 || gate_mode < 0 || gate_mode > 1 || (decay_mode == 1 && !dec)) return NV_ERR_BAD_SIZE;
+  if (gsrc && !dt_ok(gsrc_dt)) return NV_ERR_BAD_DTYPE;
   if (num_entries == 0) return NV_OK;
   DeltaArgs a;
   a.c = {cu_rows, entry_slot, S, S_stride, norm_w, out, out_dt, H, dk, dv, eps};
   a.qkv = qkv; a.C = C; a.q0 = q0; a.k0 = k0; a.v0 = v0; a.G = G;
   a.proj = proj; a.proj_dt = proj_dt; a.ld = ld; a.g0 = g0; a.b0 = b0; a.a0 = a0;
   a.A_log = A_log; a.dt_bias = dt_bias;
+  a.dec = dec; a.dec_ld = dec_ld; a.dec0 = dec0;
+  a.gsrc = gsrc ? gsrc : proj; a.gsrc_dt = gsrc ? gsrc_dt : proj_dt; a.gsrc_ld = gsrc ? gsrc_ld : ld;
+  a.decay_mode = decay_mode; a.gate_mode = gate_mode;
   const size_t smem = scan_smem(dk, dv, 2);
   int rc = allow_smem(gated_delta_scan_kernel, smem);
   if (rc) return rc;
@@ -988,13 +1156,15 @@ NV_API int nv_qk_prepare_store(const void* in, int in_dt, long long ld, int q0, 
                                const float* kw, float eps, const float* inv_freq, int rot_dim, int interleaved,
                                float amplitude, void* q_out, int q_dt, void* kc, void* vc, int cache_dt, int Hq,
                                int Hkv, int D, int Dv, int page, int write_kv, int* err, int T, int QP, int KP,
-                               int VP, cudaStream_t s) {
+                               int VP, const float* v_inv_freq, int v_rot_dim, cudaStream_t s) {
   if (!dt_ok(in_dt) || !dt_ok(q_dt) || !dt_ok(cache_dt)) return NV_ERR_BAD_DTYPE;
   if (rot_dim < 0 || rot_dim > D || rot_dim % 2 || D <= 0 || Dv <= 0) return NV_ERR_BAD_SIZE;
+  if (v_rot_dim < 0 || v_rot_dim > Dv || v_rot_dim % 2 || (v_rot_dim && !v_inv_freq)) return NV_ERR_BAD_SIZE;
   if (QP < D || KP < D || VP < Dv) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   QkArgs a = {in, in_dt, ld, q0, k0, v0, positions, row_entry, block_table, max_blocks, qw, kw, eps, inv_freq, rot_dim,
-              interleaved, amplitude, q_out, q_dt, kc, vc, cache_dt, Hq, Hkv, D, Dv, page, write_kv, err, QP, KP, VP};
+              interleaved, amplitude, q_out, q_dt, kc, vc, cache_dt, Hq, Hkv, D, Dv, page, write_kv, err, QP, KP, VP,
+              v_inv_freq, v_rot_dim};
   const size_t smem = sizeof(float) * (size_t)(QK_THREADS / 32) * D;
   int rc = allow_smem(qk_prepare_store_kernel, smem);
   if (rc) return rc;
@@ -1004,16 +1174,65 @@ NV_API int nv_qk_prepare_store(const void* in, int in_dt, long long ld, int q0, 
 
 NV_API int nv_paged_attention_general(const void* q, int q_dt, const void* kc, const void* vc, int cache_dt,
                                       const int* block_table, int max_blocks, const int* row_entry,
-                                      const int* positions, float scale, int window, int has_sink, float sink_score,
-                                      void* out, int out_dt, int T, int Hq, int Hkv, int D, int Dv, int page,
-                                      cudaStream_t s) {
+                                      const int* positions, float scale, int window, int keep_first, int has_sink,
+                                      float sink_score, const float* sinks, void* out, int out_dt, int T, int Hq,
+                                      int Hkv, int Hv, int D, int Dv, int key_span, int page, cudaStream_t s) {
   if (!dt_ok(q_dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
-  if (D > 256 || D <= 0 || Dv <= 0 || Dv > 2 * ATTG_THREADS || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
+  if (D <= 0 || Dv <= 0 || Dv > ATTG_NV * ATTG_THREADS || Hkv <= 0 || Hv <= 0 || Hq % Hv || keep_first < 0)
+    return NV_ERR_UNSUPPORTED;
+  if (key_span < 1 || (key_span == 1 && Hq % Hkv) || (key_span > 1 && key_span != Hkv)) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
-  paged_attention_general_kernel<<<dim3(T, Hq), ATTG_THREADS, 0, s>>>(q, q_dt, kc, vc, cache_dt, block_table,
-                                                                      max_blocks, row_entry, positions, scale, window,
-                                                                      has_sink, sink_score, out, out_dt, Hq, Hkv, D,
-                                                                      Dv, page);
+  const size_t smem = sizeof(float) * (size_t)key_span * D;
+  int rc = allow_smem(paged_attention_general_kernel, smem);
+  if (rc) return rc;
+  paged_attention_general_kernel<<<dim3(T, Hq), ATTG_THREADS, smem, s>>>(
+      q, q_dt, kc, vc, cache_dt, block_table, max_blocks, row_entry, positions, scale, window, keep_first, has_sink,
+      sink_score, sinks, out, out_dt, Hq, Hkv, Hv, D, Dv, key_span, page);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_mix_query_heads(const float* q, const float* mix, void* out, int out_dt, int T, int H, int G, int D,
+                              cudaStream_t s) {
+  if (!dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (H <= 0 || G <= 0 || H % G || D <= 0) return NV_ERR_BAD_SIZE;
+  if (T == 0) return NV_OK;
+  const size_t smem = sizeof(float) * ((size_t)H * D + (size_t)H * H);
+  int rc = allow_smem(mix_query_heads_kernel, smem);
+  if (rc) return rc;
+  mix_query_heads_kernel<<<T, 256, smem, s>>>(q, mix, out, out_dt, H, G, D);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_rotate_heads(const void* x, int in_dt, const int* positions, const float* inv_freq, int rot_dim,
+                           float sign, void* out, int out_dt, int T, int H, int D, cudaStream_t s) {
+  if (!dt_ok(in_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (rot_dim < 0 || rot_dim > D || rot_dim % 2 || H <= 0 || x == out) return NV_ERR_BAD_SIZE;
+  const long long total = (long long)T * H * D;
+  if (total == 0) return NV_OK;
+  rotate_heads_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, in_dt, positions, inv_freq, rot_dim, sign, out,
+                                                                      out_dt, H, D, total);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_cols_rmsnorm(const float* in, long long ld, int col0, int n, const float* w, float eps, void* out,
+                           int out_dt, int T, cudaStream_t s) {
+  if (!dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (n <= 0 || col0 < 0 || col0 + n > ld) return NV_ERR_BAD_SIZE;
+  if (T == 0) return NV_OK;
+  cols_rmsnorm_kernel<<<T, SM_THREADS, 0, s>>>(in, ld, col0, n, w, eps, out, out_dt);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_head_project(const float* x, const void* w, int w_dt, const float* gate, long long gate_ld, int gate0,
+                           void* out, int out_dt, int T, int H, int K, int N, cudaStream_t s) {
+  if (!dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (H <= 0 || K <= 0 || N <= 0) return NV_ERR_BAD_SIZE;
+  if (T == 0) return NV_OK;
+  const size_t smem = sizeof(float) * (size_t)HP_ROWS * K;
+  int rc = allow_smem(head_project_kernel, smem);
+  if (rc) return rc;
+  head_project_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H), HP_THREADS, smem, s>>>(x, w, w_dt, gate, gate_ld, gate0,
+                                                                                     out, out_dt, T, H, K, N);
   NV_RETURN_LAST();
 }
 

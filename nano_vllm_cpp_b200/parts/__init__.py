@@ -2,7 +2,7 @@
 from .base import (TensorSpec, KVCacheSpec, StateCacheSpec, CompositeCacheSpec, RunContext, Part, Norm,
                    PositionEncoding, Mixer, FeedForward, TokenInput, PartSpec)
 from .registry import register_part, build_part
-from . import norm, rotary, attention, feedforward, recurrent, parallel, token_input  # noqa: F401  (register themselves)
+from . import norm, rotary, attention, latent_attention, feedforward, recurrent, parallel, token_input  # noqa: F401  (register themselves)
 from .block import Arrangement, LayerSpec, PreNormBlock, build_layer
 from . import streams  # noqa: F401
 from .model import LayerCall, ModelSpec, Model

@@ -29,18 +29,31 @@ class PagedAttention(Mixer):
     head as projected, before its norm and rotation, is also the value head, and there is no v tensor); softmax
     weights that stay float32 in the product with the values (``exact_weights``; the tensor-core kernels of the
     default path round them to bfloat16).  ``names`` gives the tensors' names where they are not
-    the usual ones (keys: q, k, v, o, q_bias, k_bias, v_bias, o_bias, q_norm, k_norm).  A layer that uses one of
-    these options runs the general kernels (``ops.qk_prepare_store``, ``ops.paged_attention_general``).
+    the usual ones (keys: q, k, v, o, q_bias, k_bias, v_bias, o_bias, q_norm, k_norm, head_mix, sink).  A layer that
+    uses one of these options runs the general kernels (``ops.qk_prepare_store``, ``ops.paged_attention_general``).
+
+    Four more, which also run the general kernels.  ``keep_first``: with a window, the sequence's first so many
+    positions stay visible behind it (row i reads j if ``j <= i`` and ``i - j < window or j < keep_first``), at their
+    true positions; their pages are held to the request's end.  ``learned_sink``: the sink's score is a learned
+    number per query head (tensor ``sink`` [heads]).  ``head_mix``: the heads' scaled scores are mixed before mask
+    and softmax, ``s'_h = sum_g M[h, g] s_g`` with the learned ``M`` (tensor ``head_mix`` [heads, heads]); since a
+    score is linear in its query, the rows' queries are mixed instead, once per row (``ops.mix_query_heads``), and a
+    score becomes one product with all kv heads' keys side by side.  ``value_position`` (a position encoding over
+    the whole value head): the value of position j is turned by j before it is stored, and a head's output at
+    position i, the weighted sum of such values, is turned back by i, so that a value enters the output turned by
+    ``j - i``.
     """
 
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
               "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
-              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "head_mix": "head_mix", "sink": "sink"}
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, bias: bool,
                  position: PartSpec, window: int = 0, scale: float | None = None, v_head_dim: int | None = None,
                  qk_norm_eps: float | None = None, out_bias: bool = False, sink_score: float | None = None,
-                 names: dict | None = None, values_from_keys: bool = False, exact_weights: bool = False):
+                 names: dict | None = None, values_from_keys: bool = False, exact_weights: bool = False,
+                 keep_first: int = 0, learned_sink: bool = False, head_mix: bool = False,
+                 value_position: PartSpec | None = None):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden, self.Hq, self.Hkv, self.D = hidden_size, num_heads, num_kv_heads, head_dim
@@ -56,10 +69,28 @@ class PagedAttention(Mixer):
             raise ValueError("values that are the keys have the keys' head size")
         if self.values_from_keys and bias:
             raise ValueError("values that are the keys: biased projections are not supported")
-        self.general = (self.values_from_keys or bool(exact_weights) or self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
+        self.keep_first = int(keep_first) if self.window > 0 else 0
+        self.learned_sink, self.head_mix = bool(learned_sink), bool(head_mix)
+        self.value_position = (build_part("position", value_position) if isinstance(value_position, PartSpec)
+                               else value_position)
+        if self.keep_first < 0:
+            raise ValueError("keep_first must not be negative")
+        if self.learned_sink and self.sink_score is not None:
+            raise ValueError("a sink has a fixed score or a learned one, not both")
+        if self.value_position is not None:
+            vp = self.value_position
+            if self.values_from_keys or vp.pairing != "halves" or vp.amplitude != 1.0 or vp.rotary_dim > self.Dv:
+                raise ValueError("turned values: pairs (i, i + dims / 2) over at most the value head, no amplitude, and "
+                                 "values of their own")
+        # the options that only the general kernels know, whatever the dtype
+        self.extended = bool(self.keep_first or self.learned_sink or self.head_mix or self.value_position is not None)
+        self.general = (self.extended or self.values_from_keys or bool(exact_weights) or self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
                         or self.position.pairing != "halves" or self.position.amplitude != 1.0)
         if self.general:
-            if head_dim < 1 or head_dim > 256 or self.Dv < 1 or self.Dv > 256:
+            if self.extended:
+                if head_dim < 1 or self.Dv < 1 or self.Dv > 512:
+                    raise ValueError(f"value heads of {self.Dv} elements are not supported: at most 512")
+            elif head_dim < 1 or head_dim > 256 or self.Dv < 1 or self.Dv > 256:
                 raise ValueError(f"head sizes {head_dim} / {self.Dv} are not supported: the general attention kernels "
                                  "take up to 256 elements per head")
         elif head_dim % 16 or head_dim > 256:
@@ -81,6 +112,10 @@ class PagedAttention(Mixer):
         if self.qk_norm_eps is not None:
             s[n["q_norm"]] = TensorSpec((self.D,), init="ones", kind="vector")
             s[n["k_norm"]] = TensorSpec((self.D,), init="ones", kind="vector")
+        if self.head_mix:
+            s[n["head_mix"]] = TensorSpec((self.Hq, self.Hq), init="identity", kind="vector")
+        if self.learned_sink:
+            s[n["sink"]] = TensorSpec((self.Hq,), init="zeros", kind="vector")
         s.update(self.position.tensor_specs(available))      # a position encoding may have tensors of its own
         return s
 
@@ -99,7 +134,12 @@ class PagedAttention(Mixer):
         # path pads the three with zeros up to it (the scores and the sums are the same), and the output
         # projection gets zero columns for the padding.
         self.pad = 0
-        if self.general and ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and self.o_weight.dtype == torch.bfloat16:
+        self.mix_weight = fetch(n["head_mix"]).float().contiguous() if self.head_mix else None
+        self.sinks = fetch(n["sink"]).float().contiguous() if self.learned_sink else None
+        if self.value_position is not None:
+            self.value_position.load(fetch, ctx)
+        if (self.general and not self.extended and ctx.fast_kernels and ctx.act_dtype == torch.bfloat16
+                and self.o_weight.dtype == torch.bfloat16):
             self.pad = (max(self.D, self.Dv) + 15) // 16 * 16
             if self.pad != self.Dv:
                 w = torch.zeros((self.hidden, self.Hq, self.pad), dtype=self.o_weight.dtype, device=self.o_weight.device)
@@ -112,7 +152,7 @@ class PagedAttention(Mixer):
     def cache_spec(self):
         if getattr(self, "pad", 0):
             return KVCacheSpec(self.Hkv, self.pad, self.window)
-        return KVCacheSpec(self.Hkv, self.D, self.window, 0 if self.Dv == self.D else self.Dv)
+        return KVCacheSpec(self.Hkv, self.D, self.window, 0 if self.Dv == self.D else self.Dv, self.keep_first)
 
     # ------------------------------------------------------------------ forward
     def forward(self, h, batch, cache):
@@ -136,6 +176,8 @@ class PagedAttention(Mixer):
         Hq, Hkv, D, Dv = self.Hq, self.Hkv, self.D, self.Dv
         proj = linear(ctx, h, self.qkv_weight, torch.float32, bias=self.qkv_bias)
         bt = batch.block_tables[cache.group]
+        if self.extended:
+            return self._forward_extended(proj, bt, batch, cache)
         P = self.pad
         q = torch.empty((T, Hq * (P or D)), dtype=ctx.act_dtype, device=h.device)
         pos = self.position
@@ -165,6 +207,36 @@ class PagedAttention(Mixer):
         else:
             ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
                                         self.window, att, Hq, Hkv, D, Dv, sink_score=self.sink_score)
+        return linear(ctx, att, self.o_weight, torch.float32, bias=self.o_bias)
+
+    def _forward_extended(self, proj, bt, batch, cache):
+        """Kept first positions, learned sinks, mixed heads, turned values.  The queries stay float32 from the
+        projection to the scores (rotation and mixing included); scores, weights and sums are float32; keys and
+        values are in their pages in the activation dtype."""
+        ctx, T, dev = self.ctx, proj.shape[0], proj.device
+        Hq, Hkv, D, Dv = self.Hq, self.Hkv, self.D, self.Dv
+        pos, vp = self.position, self.value_position
+        q = torch.empty((T, Hq * D), dtype=torch.float32, device=dev)
+        ops.qk_prepare_store(proj, 0, Hq * D, (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
+                             self.k_norm, self.qk_norm_eps or 0.0, pos.inv_freq(), pos.rotary_dim,
+                             pos.pairing == "interleaved", pos.amplitude, q, cache.k, cache.v, Hq, Hkv, D, Dv,
+                             cache.write, ctx.err, v_inv_freq=vp.inv_freq() if vp is not None else None,
+                             v_rot_dim=vp.rotary_dim if vp is not None else 0)
+        span = 1
+        if self.head_mix:
+            span = Hkv
+            mixed = torch.empty((T, Hq * Hkv * D), dtype=torch.float32, device=dev)
+            ops.mix_query_heads(q, self.mix_weight, mixed, Hq, Hkv, D)
+            q = mixed
+        turned = vp is not None and vp.rotary_dim > 0
+        att = torch.empty((T, Hq * Dv), dtype=torch.float32 if turned else ctx.act_dtype, device=dev)
+        ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
+                                    att, Hq, Hkv, D, Dv, sink_score=self.sink_score, sinks=self.sinks,
+                                    keep_first=self.keep_first, key_span=span)
+        if turned:
+            back = torch.empty((T, Hq * Dv), dtype=ctx.act_dtype, device=dev)
+            ops.rotate_heads(att, batch.positions, vp.inv_freq(), vp.rotary_dim, -1.0, back, Hq, Dv)
+            att = back
         return linear(ctx, att, self.o_weight, torch.float32, bias=self.o_bias)
 
     def _attend(self, qkv, cache, bt, batch, att):

@@ -42,12 +42,16 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KVCacheSpec:
-    """Keys and values in pages; ``window`` > 0: only the last ``window`` positions are read.  ``v_head_dim`` > 0:
-    values have that many elements per head instead of ``head_dim``."""
+    """Keys and values in pages; ``window`` > 0: only the last ``window`` positions are read, and with
+    ``keep_first`` > 0 also the sequence's first so many positions, whose pages are then never given back.
+    ``v_head_dim`` > 0: values have that many elements per head instead of ``head_dim``.  ``values`` False: the
+    layer keeps one array per page (what it reads as values is what it reads as keys)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    keep_first: int = 0
+    values: bool = True
 
     @property
     def value_dim(self) -> int:
@@ -99,6 +103,7 @@ class Part:
 
 class Norm(Part):
     accepts_mix: bool = False        # True: ``forward`` takes a ``RowMix`` as the branch
+    accepts_sum: bool = False        # True: ``forward`` takes a ``BranchSum`` as the branch
 
     def forward(self, x, branch, want_f32: bool = False):
         raise NotImplementedError
@@ -128,6 +133,18 @@ class RowMix:
 
 
 @dataclass
+class BranchSum:
+    """Two branch outputs that are both still to be added to the residual stream (the sublayers of a layer whose
+    mixer and feed-forward read the same normed rows).  A norm with ``accepts_sum`` adds them in its own kernel;
+    for every other consumer ``resolve_branch`` adds the second into the first."""
+    first: torch.Tensor
+    second: torch.Tensor
+
+    def sum(self) -> torch.Tensor:
+        return self.first.add_(self.second)
+
+
+@dataclass
 class StreamRows:
     """What a layer hands on when nothing is left to add to the residual stream, but its rows already exist in the
     activation dtype (the layer's last kernel wrote them): a next layer that reads the stream itself takes them."""
@@ -139,6 +156,8 @@ def resolve_branch(norm: Norm, branch):
     if isinstance(branch, StreamRows):
         return None
     if isinstance(branch, RowMix) and not norm.accepts_mix:
+        return branch.sum()
+    if isinstance(branch, BranchSum) and not getattr(norm, "accepts_sum", False):
         return branch.sum()
     return branch
 

@@ -14,7 +14,7 @@ feed-forward, a post-norm block) declares its own slots and is registered like a
 """
 from __future__ import annotations
 
-from .base import PartSpec, StreamRows, resolve_branch
+from .base import PartSpec, StreamRows, BranchSum, resolve_branch
 from .registry import register_part, build_part
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "post_attention_layernorm.",
@@ -96,6 +96,26 @@ class PreNormBlock(Arrangement):
 
 
 register_part("arrangement", "prenorm", PreNormBlock)
+
+
+class ParallelBlock(Arrangement):
+    """One norm, and both sublayers read its output: ``h = norm1(x); x += mixer(h) + feed_forward(h)``.  A layer may
+    have no feed-forward.  The sum into the stream is left to whichever norm runs next, which adds both outputs in
+    its own kernel (``BranchSum``)."""
+    slots = {"norm1": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional = ("feed_forward",)
+
+    def forward(self, x, pending, batch, cache):
+        ff = self.feed_forward
+        h, h32 = self.norm1.forward(x, resolve_branch(self.norm1, pending),
+                                    want_f32=ff is not None and ff.wants_f32_input)
+        y = self.mixer.forward(h, batch, cache)
+        if ff is None:
+            return y
+        return BranchSum(y, ff.forward(h, h32, batch))
+
+
+register_part("arrangement", "parallel", ParallelBlock)
 
 
 class BranchNormBlock(Arrangement):

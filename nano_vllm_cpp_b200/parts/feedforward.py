@@ -46,26 +46,43 @@ class DenseMLP(FeedForward):
     the up product's float32 sums; its output is in the activation dtype.  Steps of few rows, and float32 runs,
     take the activation in the product's epilogue (one launch less).  A bfloat16 prompt does not: the tensor-core
     product's epilogue is the work of four to eight warps per block, and an erf per value there costs more than
-    a pass of its own (measured on 2,048 rows, 2,048 -> 8,192: 0.164 ms fused against 0.066 + 0.055 ms apart)."""
+    a pass of its own (measured on 2,048 rows, 2,048 -> 8,192: 0.164 ms fused against 0.066 + 0.055 ms apart).
+
+    ``activation="xielu"``: a learned activation with two numbers (p, q) per layer, the tensor ``act_name`` [2]:
+    ``softplus(p) z^2 + z / 2`` for z > 0 and ``(1/2 + softplus(q)) (e^z - 1 - z) + z / 2`` for z <= 0 (continuous with
+    slope 1/2 at zero).  The two factors are worked out once, in float64, when the weights are loaded; the function
+    is always a pass of its own over the up product's float32 sums."""
     FUSED_MAX_ROWS = 32
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_erf",
-                 up_name: str = "up_proj.weight", down_name: str = "down_proj.weight"):
-        if activation not in ops.EPILOGUE_ACTS:
-            raise ValueError(f"activation must be one of {sorted(ops.EPILOGUE_ACTS)}, found {activation!r}")
+                 up_name: str = "up_proj.weight", down_name: str = "down_proj.weight", act_name: str = "act"):
+        if activation not in ops.EPILOGUE_ACTS and activation != "xielu":
+            raise ValueError(f"activation must be one of {sorted(ops.EPILOGUE_ACTS) + ['xielu']}, found {activation!r}")
         self.hidden, self.inter, self.activation = hidden_size, intermediate_size, activation
-        self.up_name, self.down_name = up_name, down_name
+        self.up_name, self.down_name, self.act_name = up_name, down_name, act_name
+        self.act_params = (0.0, 0.0)
 
     def tensor_specs(self, available=None):
-        return {self.up_name: TensorSpec((self.inter, self.hidden)), self.down_name: TensorSpec((self.hidden, self.inter))}
+        s = {self.up_name: TensorSpec((self.inter, self.hidden)), self.down_name: TensorSpec((self.hidden, self.inter))}
+        if self.activation == "xielu":
+            s[self.act_name] = TensorSpec((2,), kind="vector")
+        return s
 
     def load(self, fetch, ctx):
         self.ctx = ctx
         self.up, self.down = fetch(self.up_name), fetch(self.down_name)
+        if self.activation == "xielu":
+            pq = fetch(self.act_name).double().cpu()
+            sp = torch.nn.functional.softplus(pq)
+            self.act_params = (float(sp[0]), 0.5 + float(sp[1]))
 
     def forward(self, h, h32, batch):
         ctx = self.ctx
-        if h.shape[0] <= self.FUSED_MAX_ROWS or ctx.act_dtype == torch.float32 or not ctx.fast_kernels:
+        if self.activation == "xielu":
+            z = linear(ctx, h, self.up, torch.float32)
+            act = torch.empty(z.shape, dtype=ctx.act_dtype, device=z.device)
+            ops.activation(z, act, "xielu", self.act_params)
+        elif h.shape[0] <= self.FUSED_MAX_ROWS or ctx.act_dtype == torch.float32 or not ctx.fast_kernels:
             act = linear(ctx, h, self.up, ctx.act_dtype, act=self.activation)
         else:
             z = linear(ctx, h, self.up, torch.float32)

@@ -45,6 +45,7 @@ class ModelSpec:
     streams: int = 1                    # copies of the residual stream (see parts.streams)
     logit_scale: float = 1.0            # logits = head(x) * logit_scale, then, with a cap,
     logit_softcap: float = 0.0          # logits = cap * tanh(logits / cap)
+    embed_scale: float = 1.0            # the stream starts as embed[token] * embed_scale
 
     def calls(self):
         if self.order is None:
@@ -146,7 +147,7 @@ class Model:
         ops.mark_step()
         s = self.spec
         x = torch.empty((batch.T, s.streams * s.hidden_size), dtype=torch.float32, device=ctx.device)
-        ops.embedding(batch.input_ids, self.embed, x, ctx.err, feed=ctx.feed, copies=s.streams)
+        ops.embedding(batch.input_ids, self.embed, x, ctx.err, feed=ctx.feed, copies=s.streams, scale=s.embed_scale)
         pending = None
         for i, c in enumerate(self.calls):
             pending = self.layers[c.layer].forward(x, pending, batch, cache.view(i))

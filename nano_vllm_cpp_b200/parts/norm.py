@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm, RowMix, TensorSpec
+from .base import Norm, RowMix, BranchSum, TensorSpec
 from .registry import register_part
 
 
@@ -12,9 +12,11 @@ class RMSNorm(Norm):
     """``x += branch; y = x * rsqrt(mean(x^2) + eps) * w`` (src/hip_ops.hip:395-417).
 
     The residual stream and the statistics are float32; ``y`` is written in the activation dtype.
-    A branch that is still a ``RowMix`` is summed by the same kernel.
+    A branch that is still a ``RowMix`` is summed by the same kernel, and so are the two outputs of a
+    ``BranchSum``.
     """
     accepts_mix = True
+    accepts_sum = True
 
     def __init__(self, size: int, eps: float, weight_offset: float = 0.0, weight_name: str = "weight"):
         """``weight_offset``: the stored weight lies around zero and the multiplier is ``weight_offset`` + weight
@@ -50,13 +52,16 @@ class RMSNorm(Norm):
         out32 = None
         if want_f32:
             out32 = out if out.dtype == torch.float32 else torch.empty_like(x)
-        mix = None
+        mix = branch2 = None
         if isinstance(branch, RowMix):
             if branch.index.shape[1] <= ops.ADD_RMSNORM_MAX_MIX:
                 mix, branch = branch.as_tuple(), None
             else:
                 branch = branch.sum()
-        ops.add_rmsnorm(x, branch, self.weight, self.eps, out, None if out32 is out else out32, mix=mix)
+        elif isinstance(branch, BranchSum):
+            branch, branch2 = branch.first, branch.second
+        ops.add_rmsnorm(x, branch, self.weight, self.eps, out, None if out32 is out else out32, mix=mix,
+                        branch2=branch2)
         return out, out32
 
 

@@ -87,9 +87,18 @@ class GatedDeltaRule(Mixer):
 
     Every head's ``o`` is divided by its root mean square over ``vdim`` (``eps``), multiplied by the weight ``norm``
     (one vector for all heads) and by ``silu(Wg h)``, and ``Wo`` projects back.  State per request: S and the last
-    ``taps - 1`` inputs of the convolutions."""
+    ``taps - 1`` inputs of the convolutions.
 
-    def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, conv: int, eps: float):
+    Options.  ``channel_decay``: one decay per head *and key channel*, ``g = exp(-exp(A_log_h) softplus(Wa2 (Wa1 h) +
+    dt_bias))`` laid out heads x dim (``dt_bias`` then has heads x dim entries), which multiplies the rows of S:
+    ``S = diag(g) S``; its pre-activation comes through a low-rank pair ``a1`` [r, width], ``a2`` [heads * dim, r].
+    ``low_rank_gate``: the output gate's pre-activation is ``Wg2 (Wg1 h)`` (``g1`` [r', width], ``g2``
+    [heads * vdim, r']).  The two ranks are the files' (``decay_rank`` / ``gate_rank`` say what random weights
+    take).  ``gate``: ``silu`` or ``sigmoid``."""
+
+    def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, conv: int, eps: float,
+                 channel_decay: bool = False, low_rank_gate: bool = False, gate: str = "silu",
+                 decay_rank: int | None = None, gate_rank: int | None = None):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         if conv < 1:
@@ -100,9 +109,33 @@ class GatedDeltaRule(Mixer):
         self.hidden, self.H, self.G, self.dk, self.dv, self.taps = hidden_size, heads, kv_heads, dim, vdim, conv
         self.eps = float(eps)
         self.C = 2 * kv_heads * dim + heads * vdim          # channels that pass the convolution: q | k | v
+        if gate not in ("silu", "sigmoid"):
+            raise ValueError(f"the output gate is silu or sigmoid, found {gate!r}")
+        self.channel_decay, self.low_rank_gate, self.gate = bool(channel_decay), bool(low_rank_gate), gate
+        self.decay_rank = int(decay_rank) if decay_rank else max(4, dim // 2)
+        self.gate_rank = int(gate_rank) if gate_rank else max(4, vdim // 2)
 
     def tensor_specs(self, available=None):
         W, H, G, dk, dv, taps = self.hidden, self.H, self.G, self.dk, self.dv, self.taps
+        if self.channel_decay or self.low_rank_gate:
+            from_file = available is not None       # a rank is the file's; random weights take the constructor's
+            s = {"q": TensorSpec((G * dk, W)), "q.conv": TensorSpec((G * dk, taps), kind="vector"),
+                 "k": TensorSpec((G * dk, W)), "k.conv": TensorSpec((G * dk, taps), kind="vector"),
+                 "v": TensorSpec((H * dv, W)), "v.conv": TensorSpec((H * dv, taps), kind="vector"),
+                 "b": TensorSpec((H, W)), "A_log": TensorSpec((H,), init="zeros", kind="vector"),
+                 "norm": TensorSpec((dv,), init="ones", kind="vector"), "o": TensorSpec((W, H * dv))}
+            if self.channel_decay:
+                r = None if from_file else self.decay_rank
+                s.update({"a1": TensorSpec((r, W)), "a2": TensorSpec((H * dk, r)),
+                          "dt_bias": TensorSpec((H * dk,), init="zeros", kind="vector")})
+            else:
+                s.update({"a": TensorSpec((H, W)), "dt_bias": TensorSpec((H,), init="zeros", kind="vector")})
+            if self.low_rank_gate:
+                r = None if from_file else self.gate_rank
+                s.update({"g1": TensorSpec((r, W)), "g2": TensorSpec((H * dv, r))})
+            else:
+                s["g"] = TensorSpec((H * dv, W))
+            return s
         return {"q": TensorSpec((G * dk, W)), "q.conv": TensorSpec((G * dk, taps), kind="vector"),
                 "k": TensorSpec((G * dk, W)), "k.conv": TensorSpec((G * dk, taps), kind="vector"),
                 "v": TensorSpec((H * dv, W)), "v.conv": TensorSpec((H * dv, taps), kind="vector"),
@@ -114,9 +147,41 @@ class GatedDeltaRule(Mixer):
     def load(self, fetch, ctx):
         self.ctx = ctx
         H, G, dk, dv = self.H, self.G, self.dk, self.dv
-        self.w_in = _stack([fetch("q"), fetch("k"), fetch("v"), fetch("g"), fetch("b"), fetch("a")])
         self.cols = {"q": 0, "k": G * dk, "v": 2 * G * dk}
-        self.pcols = {"g": self.C, "b": self.C + H * dv, "a": self.C + H * dv + H}
+        if self.channel_decay or self.low_rank_gate:
+            # one product for q, k, v, beta and the first halves of the low-rank pairs; the second halves follow
+            first = [fetch("q"), fetch("k"), fetch("v"), fetch("b")]
+            at = self.C + H
+            self.pcols = {"b": self.C}
+            self.a2 = self.g2 = None
+            if self.channel_decay:
+                a1, self.a2 = fetch("a1"), fetch("a2")
+                if a1.shape[0] != self.a2.shape[1]:
+                    raise ValueError(f"the decay's low-rank pair does not fit: a1 {tuple(a1.shape)}, a2 {tuple(self.a2.shape)}")
+                first.append(a1)
+                self.a1_cols = (at, at + a1.shape[0])
+                at += a1.shape[0]
+                self.pcols["a"] = 0                     # column of the second product's result
+            else:
+                first.append(fetch("a"))
+                self.pcols["a"] = at
+                at += H
+            if self.low_rank_gate:
+                g1, self.g2 = fetch("g1"), fetch("g2")
+                if g1.shape[0] != self.g2.shape[1]:
+                    raise ValueError(f"the gate's low-rank pair does not fit: g1 {tuple(g1.shape)}, g2 {tuple(self.g2.shape)}")
+                first.append(g1)
+                self.g1_cols = (at, at + g1.shape[0])
+                at += g1.shape[0]
+                self.pcols["g"] = 0
+            else:
+                first.append(fetch("g"))
+                self.pcols["g"] = at
+                at += H * dv
+            self.w_in = _stack(first)
+        else:
+            self.w_in = _stack([fetch("q"), fetch("k"), fetch("v"), fetch("g"), fetch("b"), fetch("a")])
+            self.pcols = {"g": self.C, "b": self.C + H * dv, "a": self.C + H * dv + H}
         self.w_conv = torch.cat([fetch("q.conv").float(), fetch("k.conv").float(), fetch("v.conv").float()], dim=0).contiguous()
         self.A_log, self.dt_bias = fetch("A_log"), fetch("dt_bias")
         self.norm = fetch("norm")
@@ -140,8 +205,19 @@ class GatedDeltaRule(Mixer):
         if self.taps > 1 and cache.write:
             ops.conv_state_update(proj, 0, self.C, self.taps, batch, tail)
         y = torch.empty((T, H * dv), dtype=ctx.act_dtype, device=h.device)
-        ops.gated_delta_scan(qkv, self.cols, G, proj, self.pcols, self.A_log, self.dt_bias, batch, S, H, dk, dv,
-                             self.eps, self.norm, y, columns=ctx.fast_kernels)
+        if self.channel_decay or self.low_rank_gate or self.gate != "silu":
+            # (the second halves read float32 columns of the first product's result: nothing is rounded in between)
+            dec = gsrc = None
+            if self.channel_decay:
+                dec = linear(ctx, proj[:, self.a1_cols[0]:self.a1_cols[1]], self.a2, torch.float32)
+            if self.low_rank_gate:
+                gsrc = linear(ctx, proj[:, self.g1_cols[0]:self.g1_cols[1]], self.g2, torch.float32)
+            ops.gated_delta_scan(qkv, self.cols, G, proj, self.pcols, self.A_log, self.dt_bias, batch, S, H, dk, dv,
+                                 self.eps, self.norm, y, columns=ctx.fast_kernels, channel_decay=dec, gate_src=gsrc,
+                                 gate=self.gate)
+        else:
+            ops.gated_delta_scan(qkv, self.cols, G, proj, self.pcols, self.A_log, self.dt_bias, batch, S, H, dk, dv,
+                                 self.eps, self.norm, y, columns=ctx.fast_kernels)
         return linear(ctx, y, self.w_out, torch.float32)
 
 

@@ -31,8 +31,11 @@ def check_tensors(specs: dict, found: dict) -> None:
     """``specs``: name -> TensorSpec; ``found``: name -> shape tuple."""
     missing = [n for n in specs if n not in found]
     unexpected = [n for n in found if n not in specs]
+    def fits(want, have):       # a size that the model leaves to the file is None in the spec
+        return len(want) == len(have) and all(w is None or int(w) == int(h) for w, h in zip(want, have))
+
     wrong = [(n, tuple(specs[n].shape), tuple(found[n])) for n in specs
-             if n in found and tuple(found[n]) != tuple(specs[n].shape)]
+             if n in found and not fits(tuple(specs[n].shape), tuple(found[n]))]
     if not (missing or unexpected or wrong):
         return
     lines = [f"the weights do not fit the model: {len(missing)} missing, {len(unexpected)} unexpected, "

@@ -124,18 +124,20 @@ class RequestCache:
 class CacheManager:
     def __init__(self, windows: list, num_pages, page_size: int, max_requests: int,
                  prefix_caching: bool = False, has_state: bool = False):
-        """``windows``: one entry per group (0 = reads every key; none for a model without paged layers).
+        """``windows``: one entry per group (0 = reads every key; ``(window, keep_first)``: the first ``keep_first``
+        positions stay readable behind the window; none for a model without paged layers).
         ``num_pages``: an int for all groups or a list.  ``has_state``: some layer keeps a per-request state, which
         rules prefix sharing out."""
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(windows)
-        self.windows = list(windows)
+        self.keeps = [int(w[1]) if isinstance(w, (tuple, list)) else 0 for w in windows]
+        self.windows = [int(w[0]) if isinstance(w, (tuple, list)) else int(w) for w in windows]
         self.page_size = page_size
         self.pools = [BlockPool(n, page_size) for n in num_pages]
         self.max_requests = max_requests
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: dict = {}
-        self.prefix_caching = (bool(prefix_caching) and not has_state and len(windows) == 1 and windows[0] == 0)
+        self.prefix_caching = (bool(prefix_caching) and not has_state and len(windows) == 1 and self.windows[0] == 0)
 
     # ------------------------------------------------------------------ requests
     def has(self, rid) -> bool:
@@ -172,6 +174,10 @@ class CacheManager:
             return 0
         return max(0, start + 1 - w) // self.page_size
 
+    def _kept_pages(self, g: int) -> int:
+        """Pages that hold one of the group's kept first positions: a request holds them to its end."""
+        return -(-max(0, self.keeps[g]) // self.page_size) if self.windows[g] > 0 else 0
+
     def pages_needed(self, rid, start: int, end: int) -> list:
         """Per group: pages to take minus pages that running rows [start, end) gives back first."""
         rc = self.requests[rid]
@@ -180,7 +186,7 @@ class CacheManager:
             total = (end + self.page_size - 1) // self.page_size
             fresh = max(0, total - len(table))
             first = self._first_needed_page(g, start)
-            back = sum(1 for p in table[:first] if p >= 0 and self.pools[g].ref_count[p] == 1)
+            back = sum(1 for p in table[self._kept_pages(g):first] if p >= 0 and self.pools[g].ref_count[p] == 1)
             need.append(fresh - back)
         return need
 
@@ -196,7 +202,7 @@ class CacheManager:
             raise RuntimeError(f"request {rid!r}: rows start at {start} but {rc.num_tokens} tokens are cached")
         for g, table in enumerate(rc.tables):
             first = min(self._first_needed_page(g, start), len(table))
-            for i in range(first):
+            for i in range(self._kept_pages(g), first):
                 if table[i] >= 0:
                     self.pools[g].release(table[i])
                     table[i] = -1
