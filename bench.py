@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design bizodra|kifunex [--design-sizes s,m]     (another measurement, see ``design_bench``)
+    python bench.py --design bizodra|kifunex|sanesun [--design-sizes s,m]     (another measurement, see ``design_bench``)
 
 Default run: the layer sizes of the Qwen1.5-MoE-A2.7B shape with random bfloat16 weights, a batch
 of 8 sequences each at a 2,048-token context; a step is one decode step of that batch.  ``value``
@@ -265,8 +265,25 @@ def sparse_qwen_config(z):
                 rms_norm_eps=1e-6, max_position_embeddings=32768, tie_word_embeddings=False, qkv_bias=True)
 
 
+# --design sanesun: the same measurement for the Sanesun decoder beside the closest existing model at equal size: the
+# Bizodra decoder (the other one whose layers mix matrix memories with attention around a dense MLP) with the same
+# width, depth, heads, head size, MLP width and vocabulary.  Sanesun's layers go latent attention, delta rule, window
+# attention, delta rule.
+def sanesun_config(z):
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    latent = {"heads": H, "dim": D, "vdim": D, "q_rank": W // 2, "kv_rank": 256, "scale": D ** -0.5}
+    delta = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+    window = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+              "mask": {"size": 1024, "keep_first": 4}, "rot": {"dims": D // 2, "base": 1e6}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    kinds = [("latent_attention", latent), ("channel_delta", delta), ("attention", window), ("channel_delta", delta)]
+    return {"architecture": "Sanesun", "vocab": z["vocab"], "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(z["layers"])]}
+
+
 DESIGNS = {"bizodra": (DESIGN_SIZES, "bizodra", bizodra_config, "qwen2_dense", dense_qwen_config),
-           "kifunex": (KIFUNEX_SIZES, "kifunex", kifunex_config, "qwen2_moe", sparse_qwen_config)}
+           "kifunex": (KIFUNEX_SIZES, "kifunex", kifunex_config, "qwen2_moe", sparse_qwen_config),
+           "sanesun": (DESIGN_SIZES, "sanesun", sanesun_config, "bizodra", bizodra_config)}
 
 
 def design_bench(args) -> int:
@@ -421,7 +438,8 @@ def _fill_caches(views, torch):
             _fill_caches(v.parts, torch)
         elif v.kind == "kv" and v.write:
             v.k.normal_(0, 0.5)
-            v.v.normal_(0, 0.5)
+            if v.v is not None:              # a layer that keeps one array per page has no values
+                v.v.normal_(0, 0.5)
         elif v.kind == "state" and v.write:
             v.state.normal_(0, 0.05)
 

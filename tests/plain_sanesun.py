@@ -150,12 +150,19 @@ def dense_mlp(h, W, p):
 
 
 # ------------------------------------------------------------------------------ the model
+def kind_of(layer_type):
+    """``attention_2`` is an attention layer with a further set of sizes."""
+    head, _, tail = layer_type.rpartition("_")
+    return head if head and tail.isdigit() else layer_type
+
+
 def mixer(L, h, W, p, eps):
-    if L["type"] == "channel_delta":
+    kind = kind_of(L["type"])
+    if kind == "channel_delta":
         return channel_delta(h, W, p, L["mixer"], eps)
-    if L["type"] == "attention":
+    if kind == "attention":
         return window_attention(h, W, p, L["mixer"])
-    if L["type"] == "latent_attention":
+    if kind == "latent_attention":
         return latent_attention(h, W, p, L["mixer"], eps)
     raise ValueError(L["type"])
 
@@ -194,7 +201,8 @@ def tensor_shapes(cfg):
         p, m = f"l{i}.", L["mixer"]
         x = p + "mix."
         out[p + "norm1"] = ((Wd,), "o")
-        if L["type"] == "channel_delta":
+        kind = kind_of(L["type"])
+        if kind == "channel_delta":
             H, G, dk, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
             r = m.get("rank", max(4, dk // 2))
             out.update({x + "q": ((G * dk, Wd), "w"), x + "q.conv": ((G * dk, taps), "c"),
@@ -203,12 +211,12 @@ def tensor_shapes(cfg):
                         x + "b": ((H, Wd), "w"), x + "A_log": ((H,), "a"), x + "norm": ((dv,), "o"),
                         x + "a1": ((r, Wd), "w"), x + "a2": ((H * dk, r), "w"), x + "dt_bias": ((H * dk,), "d"),
                         x + "g1": ((r + 1, Wd), "w"), x + "g2": ((H * dv, r + 1), "w"), x + "o": ((Wd, H * dv), "w")})
-        elif L["type"] == "attention":
+        elif kind == "attention":
             H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
             out.update({x + "q": ((H * D, Wd), "w"), x + "q.b": ((H * D,), "z"), x + "k": ((G * D, Wd), "w"),
                         x + "k.b": ((G * D,), "z"), x + "v": ((G * Dv, Wd), "w"), x + "v.b": ((G * Dv,), "z"),
                         x + "talk": ((H, H), "t"), x + "sink": ((H,), "s"), x + "o": ((Wd, H * Dv), "w")})
-        elif L["type"] == "latent_attention":
+        elif kind == "latent_attention":
             H, D, Dv, rk, rq = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["q_rank"]
             out.update({x + "dq": ((rq, Wd), "w"), x + "dq.norm": ((rq,), "o"), x + "uq": ((H * D, rq), "w"),
                         x + "dkv": ((rk, Wd), "w"), x + "dkv.norm": ((rk,), "o"), x + "uk": ((H * D, rk), "w"),
@@ -278,3 +286,36 @@ def write_folder(cfg, W, out_dir):
         for b in blobs:
             f.write(b)
     return out_dir
+
+
+# ------------------------------------------------------------------------------ configurations of our own
+def delta_layer(heads, kv_heads, dim, vdim, conv, ff=0, rank=None, kind="channel_delta"):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+    if rank is not None:
+        m["rank"] = rank
+    return {"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def attention_layer(heads, kv_heads, dim, vdim, window, keep_first, rot_dims, base, scale, ff=0, kind="attention"):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale,
+         "mask": {"size": window, "keep_first": keep_first}, "rot": {"dims": rot_dims, "base": base}}
+    return {"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def latent_layer(heads, dim, vdim, q_rank, kv_rank, scale, ff=0, kind="latent_attention"):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale}
+    return {"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def model_config(layers, width, vocab, eps=1e-6, embed_scale=None):
+    cfg = {"architecture": "Sanesun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if embed_scale is not None:
+        cfg["embedding"] = {"scale": embed_scale}
+    return cfg
+
+
+def mixer_weights(layer, width, seed, prefix="m."):
+    """The tensors of one mixer alone, named ``<prefix><tensor>``."""
+    cfg = model_config([dict(layer, mlp=None)], width, 8)
+    W = random_weights(cfg, seed)
+    return {k.replace("l0.mix.", prefix): v for k, v in W.items() if k.startswith("l0.mix.")}
