@@ -840,8 +840,7 @@ def col_scan_usable(dk: int, dv: int) -> bool:
 
 def channel_scan_usable(dk: int, dv: int) -> bool:
     """Whether the fast form of the delta rule with channel decays takes these sizes (else the plain scan runs)."""
-    fn = getattr(lib(), "nv_channel_scan_usable", None)
-    return bool(fn(dk, dv)) if fn is not None else False
+    return bool(lib().nv_channel_scan_usable(dk, dv))
 
 
 def mlstm_scan(proj, cols: dict, batch, S, n, m, H: int, dk: int, dv: int, cap: float, eps: float, norm_w, out,
@@ -893,12 +892,15 @@ def gated_delta_scan(qkv, cols: dict, G: int, proj, pcols: dict, A_log, dt_bias,
         _need(gs.stride(-1) == 1 and gs.shape[0] == qkv.shape[0], "gated_delta_scan: gate rows")
         if columns and col_scan_usable(dk, dv) and dec is not None and channel_scan_usable(dk, dv):
             T = qkv.shape[0]
+            raw = torch.empty((T, H, dv), dtype=torch.float32, device=qkv.device)
+            gate_buf = torch.empty((T, H, 2), dtype=torch.float32, device=qkv.device)
+            decays = torch.empty((T, H * dk), dtype=torch.float32, device=qkv.device)
             _check(lib().nv_channel_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj),
                                                dt(proj), proj.stride(0), pcols["b"], _p(dec), dec.stride(0), pcols["a"],
                                                _p(gs), dt(gs), gs.stride(0), pcols["g"], (1 if gate == "sigmoid" else 0),
                                                _p(A_log), _p(dt_bias), _p(batch.cu_rows), _p(batch.entry_slot), _p(S),
-                                               _slot_stride(S), H, dk, dv, eps, _p(norm_w), _p(out), dt(out), batch.S,
-                                               T, _stream()), "channel_delta_scan")
+                                               _slot_stride(S), H, dk, dv, eps, _p(norm_w), _p(raw), _p(gate_buf),
+                                               _p(decays), _p(out), dt(out), batch.S, T, _stream()), "channel_delta_scan")
             return
         _check(lib().nv_gated_delta_scan(_p(qkv), qkv.shape[1], cols["q"], cols["k"], cols["v"], G, _p(proj), dt(proj),
                                          proj.stride(0), pcols["g"], pcols["b"], (0 if dec is not None else pcols["a"]),
@@ -1020,15 +1022,15 @@ def cols_rmsnorm(src, col0: int, n: int, w, eps: float, out) -> None:
 
 
 def head_project(x, w, out, H: int, K: int, N: int, gate=None, gate_col: int = 0) -> None:
-    """``out[t, h, :] = x[t, h, :] @ w[h]`` for float32 ``x`` [T, H * K] and ``w`` [H, K, N]; with ``gate`` (float32
+    """``out[t, h, :] = x[t, h, :] @ w[h]`` for ``x`` [T, H * K] and ``w`` [H, K, N]; with ``gate`` (float32
     rows, column ``gate_col + h``) the head's output is multiplied by the sigmoid of its gate."""
     _cuda_contig(x, w, out)
-    _f32(x, gate)
+    _f32(gate)
     T = x.shape[0]
     _need(x.shape == (T, H * K) and w.shape == (H, K, N) and out.shape == (T, H * N), "head_project: shapes")
     _need(gate is None or (gate.stride(-1) == 1 and gate.shape[0] == T and gate.shape[1] >= gate_col + H),
           "head_project: gate rows")
-    _check(lib().nv_head_project(_p(x), _p(w), dt(w), _p(gate), (gate.stride(0) if gate is not None else 0), gate_col,
+    _check(lib().nv_head_project(_p(x), dt(x), _p(w), dt(w), _p(gate), (gate.stride(0) if gate is not None else 0), gate_col,
                                  _p(out), dt(out), T, H, K, N, _stream()), "head_project")
 
 

@@ -675,14 +675,14 @@ __global__ void __launch_bounds__(SM_THREADS) cols_rmsnorm_kernel(const float* _
 }
 
 // ------------------------------------------------------------------ a small product per head
-// x [T, H, K] float32, w [H, K, N] (float32 or bfloat16) -> out [T, H, N] = x[t, h, :] w[h]; with `gate` the head's
+// x [T, H, K] (float32 or bfloat16), w [H, K, N] (float32 or bfloat16) -> out [T, H, N] = x[t, h, :] w[h]; with `gate` the head's
 // output is multiplied by sigmoid(gate[t, gate0 + h]).  A block takes HP_ROWS rows of one head, so a weight is read
 // once for all of them; a thread owns output columns and sums over k in ascending order.
 constexpr int HP_ROWS = 8;
 constexpr int HP_THREADS = 128;
 
-__global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const float* __restrict__ x, const void* __restrict__ w,
-                                                                  int w_dt, const float* __restrict__ gate,
+__global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const void* __restrict__ x, int x_dt,
+                                                                  const void* __restrict__ w, int w_dt, const float* __restrict__ gate,
                                                                   long long gate_ld, int gate0, void* __restrict__ out,
                                                                   int out_dt, int T, int H, int K, int N) {
   extern __shared__ float xs[];      // HP_ROWS * K
@@ -690,7 +690,7 @@ __global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const float* _
   const int rows = min(HP_ROWS, T - t0);
   for (int i = threadIdx.x; i < HP_ROWS * K; i += HP_THREADS) {
     const int r = i / K, k = i % K;
-    xs[i] = r < rows ? x[((size_t)(t0 + r) * H + h) * K + k] : 0.f;
+    xs[i] = r < rows ? ld_dt(x, x_dt, ((size_t)(t0 + r) * H + h) * K + k) : 0.f;
   }
   __syncthreads();
   float g[HP_ROWS];
@@ -752,6 +752,8 @@ struct ColArgs {
   float* raw;
   int RW, H, dk, dv;
   int vec16;                // q and k can be copied sixteen bytes at a time (set by the launcher from the addresses)
+  const float* dec;         // delta rule with channel decays (MODE 2): the decays themselves, [T, dec_ld], head h's at h * dk
+  long long dec_ld;
 };
 
 // The gates of a row and head, ready for the recurrence: the matrix LSTM's capped log gates (i, f), or the delta
@@ -796,7 +798,9 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int COL_RING = 8;             // rows in flight: a row's q, k, v and gates are asked for this many rows ahead
 
-template <int DK, int MODE, bool PRE>   // MODE 0: matrix LSTM, 1: gated delta rule; PRE: the gates come ready
+// MODE 0: matrix LSTM, 1: gated delta rule, 2: delta rule with a decay per key channel (its decays come ready, a
+// row of dk numbers per row and head, and ride in the ring beside q and k); PRE: the gates come ready
+template <int DK, int MODE, bool PRE>
 __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   // A ring of rows in shared memory, filled by asynchronous copies several rows ahead of the row that is computed:
   // with one row ahead every row waited for its loads' way through the memory system.
@@ -806,6 +810,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   constexpr int COL_COLS = COL_THREADS / COL_RSPLIT; // columns of a block
   __shared__ float vs[COL_RING][COL_COLS];
   __shared__ float gs[COL_RING][2];
+  __shared__ __align__(16) float ds[MODE == 2 ? COL_RING : 1][DK];
   constexpr int PER = DK / COL_THREADS > 0 ? DK / COL_THREADS : 1;
   constexpr int DKH = COL_ROWS;                      // rows of a column that one thread holds
   const int e = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -833,7 +838,10 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   for (int r = 0; r < DKH; ++r) Sreg[r] = (active && row_of(r) < dk) ? colp[(size_t)row_of(r) * cstride] : 0.f;
   float m = 0.f, rate = 0.f, dtb = 0.f;
   if (MODE == 0) m = a.m[(size_t)slot * a.m_stride + h];
-  else { rate = expf(a.A_log[h]); dtb = a.dt_bias[h]; }
+  else if (MODE == 1) { rate = expf(a.A_log[h]); dtb = a.dt_bias[h]; }
+  if (MODE == 2)
+    for (int i = tid; i < COL_RING * DK; i += COL_THREADS)
+      if (i % DK >= dk) ds[i / DK][i % DK] = 0.f;
   // what no copy ever writes: the rows of q and k beyond dk, the value of the normaliser's column and of no column
   for (int i = tid; i < COL_RING * DK; i += COL_THREADS)
     if (i % DK >= dk) { qs[i / DK][i % DK] = 0.f; ks[i / DK][i % DK] = 0.f; }
@@ -853,13 +861,23 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
   const bool does_16 = a.vec16 && tid < 2 * Q4 && 4 * piece < dk;
   const float* src_v = a.vsrc + (size_t)row0 * a.v_ld + a.v0 + h * dv + (has_v ? c : 0);
   const float* src_g = gates + (size_t)row0 * a.gates_ld + (tid == 1 ? a.gb0 : a.ga0) + (PRE ? 2 * h : h);
+  const float* src_d = MODE == 2 ? a.dec + (size_t)row0 * a.dec_ld + (size_t)h * dk + (a.vec16 ? 4 * tid : tid) : nullptr;
+  const bool d_16 = MODE == 2 && a.vec16 && tid < Q4 && 4 * tid < dk;
   int fetch_slot = 0;
   auto fetch = [&](int t) {
     if (t < row1) {
       const int b = fetch_slot;
       if (a.vec16) {
         if (does_16) cp_async16((k_side ? ks[b] : qs[b]) + 4 * piece, src_16);
+        if (d_16) cp_async16(ds[b] + 4 * tid, src_d);
       } else {
+        if (MODE == 2) {
+#pragma unroll
+          for (int i = 0; i < PER; ++i) {
+            const int r = tid + i * COL_THREADS;
+            if (r < dk && r < DK) cp_async4(&ds[b][r], src_d + i * COL_THREADS);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
           const int r = tid + i * COL_THREADS;
@@ -872,6 +890,7 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
       if (has_v) cp_async4(&vs[b][cl], src_v);
       if (tid < 2) cp_async4(&gs[b][tid], src_g);
       src_q += a.qk_ld; src_k += a.qk_ld; src_16 += a.qk_ld; src_v += a.v_ld; src_g += a.gates_ld;
+      if (MODE == 2) src_d += a.dec_ld;
       fetch_slot = (fetch_slot + 1) % COL_RING;
     }
     cp_async_commit();                               // (a group per row, also an empty one: the count below relies on it)
@@ -908,6 +927,37 @@ __global__ void __launch_bounds__(COL_THREADS) col_scan_kernel(ColArgs a) {
       for (int off = 1; off < COL_RSPLIT; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);   // same sum in every lane
       if (active && half == 0) out[c] = acc * a.q_scale;     // q's scale, taken out of the sum
       if (blockIdx.z == 0 && tid == 0) out[dv + 1] = m;
+    } else if (MODE == 2) {
+      // S_r <- g_r S_r;  u = beta (v - sum_r S_r k_r);  S_r += k_r u;  o = sum_r S_r q_r = sum_r (g_r S_r) q_r + (k . q) u
+      const float beta = ga;
+      const float4* d4 = reinterpret_cast<const float4*>(ds[b]) + half;
+      float ak = 0.f, aq = 0.f, kq = 0.f, ak1 = 0.f, aq1 = 0.f, kq1 = 0.f;
+#pragma unroll
+      for (int r4 = 0; r4 < DKH / 4; ++r4) {
+        const float4 qq = q4[COL_RSPLIT * r4], kk = k4[COL_RSPLIT * r4], dd = d4[COL_RSPLIT * r4];
+        float x;
+        x = dd.x * Sreg[4 * r4 + 0]; Sreg[4 * r4 + 0] = x; ak = fmaf(x, kk.x, ak); aq = fmaf(x, qq.x, aq); kq = fmaf(kk.x, qq.x, kq);
+        x = dd.y * Sreg[4 * r4 + 1]; Sreg[4 * r4 + 1] = x; ak1 = fmaf(x, kk.y, ak1); aq1 = fmaf(x, qq.y, aq1); kq1 = fmaf(kk.y, qq.y, kq1);
+        x = dd.z * Sreg[4 * r4 + 2]; Sreg[4 * r4 + 2] = x; ak = fmaf(x, kk.z, ak); aq = fmaf(x, qq.z, aq); kq = fmaf(kk.z, qq.z, kq);
+        x = dd.w * Sreg[4 * r4 + 3]; Sreg[4 * r4 + 3] = x; ak1 = fmaf(x, kk.w, ak1); aq1 = fmaf(x, qq.w, aq1); kq1 = fmaf(kk.w, qq.w, kq1);
+      }
+      ak += ak1; aq += aq1; kq += kq1;
+#pragma unroll
+      for (int off = 1; off < COL_RSPLIT; off <<= 1) {
+        ak += __shfl_xor_sync(0xffffffffu, ak, off);
+        aq += __shfl_xor_sync(0xffffffffu, aq, off);
+        kq += __shfl_xor_sync(0xffffffffu, kq, off);
+      }
+      const float u = beta * (v - ak);
+      if (active && half == 0) out[c] = fmaf(kq, u, aq) * a.q_scale;
+#pragma unroll
+      for (int r4 = 0; r4 < DKH / 4; ++r4) {
+        const float4 kk = k4[COL_RSPLIT * r4];
+        Sreg[4 * r4 + 0] = fmaf(kk.x, u, Sreg[4 * r4 + 0]);
+        Sreg[4 * r4 + 1] = fmaf(kk.y, u, Sreg[4 * r4 + 1]);
+        Sreg[4 * r4 + 2] = fmaf(kk.z, u, Sreg[4 * r4 + 2]);
+        Sreg[4 * r4 + 3] = fmaf(kk.w, u, Sreg[4 * r4 + 3]);
+      }
     } else {
       float beta = ga, g = gb;
       if (!PRE) scan_gates(1, ga, gb, 0.f, rate, dtb, beta, g);
@@ -970,6 +1020,24 @@ __global__ void __launch_bounds__(256) head_finish_kernel(const float* __restric
     const float gv = ld_dt(gate, gate_dt, (size_t)t * gate_ld + g0 + h * dv + i);
     const float act = gate_act == 0 ? sigmoidf_(gv) : siluf_(gv);
     st_dt(out, out_dt, (size_t)t * H * dv + (size_t)h * dv + i, x[i] * inv * r * w[w_per_head ? h * dv + i : i] * act);
+  }
+}
+
+// Before the scan with channel decays: decays[t, h dk + r] = exp(-exp(A_log[h]) softplus(pre[t, dec0 + h dk + r] +
+// dt_bias[h dk + r])) and gates[t, h] = (sigmoid(beta's pre-activation), 1), all float32.
+__global__ void channel_gates_kernel(const float* __restrict__ pre, long long pre_ld, int dec0,
+                                     const void* __restrict__ proj, int proj_dt, long long proj_ld, int b0,
+                                     const float* __restrict__ A_log, const float* __restrict__ dt_bias, int H, int dk,
+                                     float* __restrict__ decays, float* __restrict__ gates, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int hd = H * dk;
+  const long long t = i / hd;
+  const int c = (int)(i % hd), h = c / dk;
+  decays[i] = expf(-expf(A_log[h]) * softplusf_(pre[t * pre_ld + dec0 + c] + dt_bias[c]));
+  if (c % dk == 0) {
+    gates[2 * (t * H + h)] = sigmoidf_(ld_dt(proj, proj_dt, (size_t)t * proj_ld + b0 + h));
+    gates[2 * (t * H + h) + 1] = 1.f;
   }
 }
 
@@ -1223,20 +1291,21 @@ NV_API int nv_cols_rmsnorm(const float* in, long long ld, int col0, int n, const
   NV_RETURN_LAST();
 }
 
-NV_API int nv_head_project(const float* x, const void* w, int w_dt, const float* gate, long long gate_ld, int gate0,
+NV_API int nv_head_project(const void* x, int x_dt, const void* w, int w_dt, const float* gate, long long gate_ld, int gate0,
                            void* out, int out_dt, int T, int H, int K, int N, cudaStream_t s) {
-  if (!dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (!dt_ok(x_dt) || !dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (H <= 0 || K <= 0 || N <= 0) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   const size_t smem = sizeof(float) * (size_t)HP_ROWS * K;
   int rc = allow_smem(head_project_kernel, smem);
   if (rc) return rc;
-  head_project_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H), HP_THREADS, smem, s>>>(x, w, w_dt, gate, gate_ld, gate0,
+  head_project_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H), HP_THREADS, smem, s>>>(x, x_dt, w, w_dt, gate, gate_ld, gate0,
                                                                                      out, out_dt, T, H, K, N);
   NV_RETURN_LAST();
 }
 
 NV_API int nv_col_scan_usable(int dk, int dv) { return dk >= 1 && dk <= 128 && dv >= 1; }
+NV_API int nv_channel_scan_usable(int dk, int dv) { return nv_col_scan_usable(dk, dv); }
 
 // The matrix LSTM through col_scan_kernel; raw: [T, H, dv + 2] and gate_buf: [T, H, 2] float32 scratch.
 NV_API int nv_mlstm_col_scan(const float* proj, long long ld, int q0, int k0, int v0, int g0, int i0, int f0,
@@ -1281,5 +1350,40 @@ NV_API int nv_gated_delta_col_scan(const float* qkv, int C, int q0, int k0, int 
   const long long items = (long long)T * H;
   head_finish_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>(raw, dv, 0, 0.f, proj, proj_dt, ld, g0, 1, norm_w, 0,
                                                                  eps, out, out_dt, T, H, dv);
+  NV_RETURN_LAST();
+}
+
+// The delta rule with a decay per head and key channel through col_scan_kernel.  `dec` [T, dec_ld] float32 holds the
+// decays' pre-activations at column dec0 (head h's at dec0 + h dk); `gsrc` the output gate's at g0, gate_mode 1: a
+// sigmoid, 0: silu.  Scratch, all float32: raw [T, H, dv], gate_buf [T, H, 2], decays [T, H dk].
+NV_API int nv_channel_delta_scan(const float* qkv, int C, int q0, int k0, int v0, int G, const void* proj, int proj_dt,
+                                 long long ld, int b0, const float* dec, long long dec_ld, int dec0, const void* gsrc,
+                                 int gsrc_dt, long long gsrc_ld, int g0, int gate_mode, const float* A_log,
+                                 const float* dt_bias, const int* cu_rows, const int* entry_slot, float* S,
+                                 long long S_stride, int H, int dk, int dv, float eps, const float* norm_w, float* raw,
+                                 float* gate_buf, float* decays, void* out, int out_dt, int num_entries, int T,
+                                 cudaStream_t s) {
+  if (!dt_ok(out_dt) || !dt_ok(proj_dt) || !dt_ok(gsrc_dt)) return NV_ERR_BAD_DTYPE;
+  if (!nv_channel_scan_usable(dk, dv) || H <= 0 || G <= 0 || H % G) return NV_ERR_UNSUPPORTED;
+  if (!dec || !raw || !gate_buf || !decays || gate_mode < 0 || gate_mode > 1) return NV_ERR_BAD_SIZE;
+  if (num_entries == 0 || T == 0) return NV_OK;
+  const long long n = (long long)T * H * dk;
+  channel_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(dec, dec_ld, dec0, proj, proj_dt, ld, b0, A_log,
+                                                                  dt_bias, H, dk, decays, gate_buf, n);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  ColArgs a = {};
+  a.cu_rows = cu_rows; a.entry_slot = entry_slot; a.S = S; a.S_stride = S_stride; a.qk = qkv; a.qk_ld = C; a.q0 = q0;
+  a.k0 = k0; a.G = G; a.vsrc = qkv; a.v_ld = C; a.v0 = v0; a.gates = gate_buf; a.gates_dt = NV_DT_F32;
+  a.gates_ld = 2LL * H; a.ga0 = 0; a.gb0 = 1; a.A_log = A_log; a.dt_bias = dt_bias; a.q_scale = 1.f; a.raw = raw;
+  a.RW = dv; a.H = H; a.dk = dk; a.dv = dv; a.dec = decays; a.dec_ld = (long long)H * dk;
+  a.vec16 = (((uintptr_t)qkv & 15) == 0 && C % 4 == 0 && q0 % 4 == 0 && k0 % 4 == 0 && dk % 4 == 0 &&
+             ((uintptr_t)decays & 15) == 0) ? 1 : 0;
+  int rc = launch_col_scan_p<2, true>(a, num_entries, s);
+  if (rc) return rc;
+  const long long items = (long long)T * H;
+  head_finish_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>(raw, dv, 0, 0.f, gsrc, gsrc_dt, gsrc_ld, g0,
+                                                                 gate_mode == 1 ? 0 : 1, norm_w, 0, eps, out, out_dt, T,
+                                                                 H, dv);
   NV_RETURN_LAST();
 }

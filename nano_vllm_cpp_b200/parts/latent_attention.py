@@ -76,11 +76,30 @@ class LatentAttention(Mixer):
         cq = torch.empty((T, rq), dtype=ctx.act_dtype, device=dev)
         ops.cols_rmsnorm(down, 0, rq, self.dq_norm, self.eps, cq)
         q = linear(ctx, cq, self.w_uq, torch.float32)
-        q_lat = torch.empty((T, H * rk), dtype=torch.float32, device=dev)
+        # A bfloat16 run whose latent is a head size of the tensor-core kernels attends through them: one shared
+        # "kv head" of kv_rank elements whose pages are keys and values at once (single rows through the split-key
+        # decode kernel, the others through the prompt kernel; the softmax weights keep their float32 bits in the
+        # product with the values, as three bfloat16 terms).  Else the general kernel, all float32.
+        fast = (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+                and rk % 16 == 0 and rk <= 256)
+        mid = torch.bfloat16 if fast else torch.float32
+        q_lat = torch.empty((T, H * rk), dtype=mid, device=dev)
         ops.head_project(q, self.w_uk, q_lat, H, D, rk)
-        lat = torch.empty((T, H * rk), dtype=torch.float32, device=dev)
-        ops.paged_attention_general(q_lat, cache.k, None, bt, batch.row_entry, batch.positions, self.scale, 0, lat,
-                                    H, 1, rk, rk)
+        lat = torch.empty((T, H * rk), dtype=mid, device=dev)
+        if fast:
+            single = batch.n_single if ops.attention_decode_usable(cache.k, rk) else 0
+            if single:
+                ops.attention_decode(q_lat, cache.k, cache.k, bt, batch.row_entry, batch.positions, self.scale, 0, lat,
+                                     H, 1, rk, batch.max_context if batch.decode_only else batch.max_single_context,
+                                     rows=None if batch.decode_only else batch.single_rows, err=ctx.err,
+                                     float_weights=True)
+            if single < batch.S:
+                tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
+                ops.attention_prefill(q_lat, cache.k, cache.k, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
+                                      0, lat, H, 1, rk, err=ctx.err, min_rows=2 if single else 1, weight_terms=3)
+        else:
+            ops.paged_attention_general(q_lat, cache.k, None, bt, batch.row_entry, batch.positions, self.scale, 0, lat,
+                                        H, 1, rk, rk)
         o = torch.empty((T, H * Dv), dtype=ctx.act_dtype, device=dev)
         ops.head_project(lat, self.w_uv, o, H, rk, Dv, gate=down if self.output_gate else None, gate_col=rq + rk)
         return linear(ctx, o, self.w_out, torch.float32)
