@@ -458,6 +458,42 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
                                   weight_terms, _stream()), "attention_prefill")
 
 
+def attention_prefill_wide_usable(D: int, key_span: int, Dv: int) -> bool:
+    """Whether ``attention_prefill_wide`` takes these sizes: a key length ``key_span * D`` up to 512 and values up to
+    256, both multiples of 16."""
+    return bool(lib().nv_attention_prefill_wide_usable(D, key_span, Dv))
+
+
+def attention_prefill_wide_tile_rows() -> int:
+    return int(lib().nv_attention_prefill_wide_tile_rows())
+
+
+def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
+                           window: int, out, Hq: int, Hkv: int, D: int, Dv: int, *, keep_first: int = 0, sinks=None,
+                           key_span: int = 1, min_rows: int = 1) -> None:
+    """bfloat16 rows of any mix of portions (single rows too) against paged keys of ``D`` and values of ``Dv``
+    elements, on the tensor cores with float32 softmax weights (three bfloat16 terms).  ``q`` [T, Hq * key_span * D]:
+    with ``key_span`` = Hkv > 1 a query head is scored against all kv heads' keys side by side (queries mixed across
+    heads).  ``keep_first``: the first so many positions stay visible behind the window; ``sinks`` [Hq] float32: a
+    learned score without key and value in every softmax.  ``out`` [T, Hq * Dv] bfloat16 or float32."""
+    _cuda_contig(q, k_cache, v_cache, block_table, cu_rows, entry_pos0, out, sinks)
+    _i32(block_table, cu_rows, entry_pos0)
+    _f32(sinks)
+    T = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16,
+          "attention_prefill_wide: bfloat16 only")
+    _need(out.dtype in (torch.bfloat16, torch.float32) and out.shape == (T, Hq * Dv) and q.shape == (T, Hq * key_span * D),
+          "attention_prefill_wide: shapes")
+    _need(k_cache.shape[1] == Hkv and k_cache.shape[3] == D and v_cache.shape[3] == Dv and key_span in (1, Hkv),
+          "attention_prefill_wide: cache shapes")
+    _need(sinks is None or sinks.numel() == Hq, "attention_prefill_wide: one sink per head")
+    _check(lib().nv_attention_prefill_wide(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
+                                           _p(cu_rows), _p(entry_pos0), entry_pos0.numel(), max_tiles, scale, window,
+                                           keep_first, _p(sinks), _p(out), (1 if out.dtype == torch.float32 else 0), Hq,
+                                           Hkv, v_cache.shape[1], D, key_span, Dv, k_cache.shape[2], min_rows,
+                                           _stream()), "attention_prefill_wide")
+
+
 def gemm_plain_tile_m() -> int:
     return int(lib().nv_gemm_plain_tile_m())
 

@@ -216,23 +216,33 @@ class PagedAttention(Mixer):
         ctx, T, dev = self.ctx, proj.shape[0], proj.device
         Hq, Hkv, D, Dv = self.Hq, self.Hkv, self.D, self.Dv
         pos, vp = self.position, self.value_position
-        q = torch.empty((T, Hq * D), dtype=torch.float32, device=dev)
+        span = Hkv if self.head_mix else 1
+        # A bfloat16 run whose sizes the tensor-core kernel takes goes there with all its entries, single rows too:
+        # the queries are rounded to bfloat16 once, after rotation and mixing.  Else the general kernel, float32
+        # queries against the pages.
+        fast = (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+                and self.sink_score is None and self.scale > 0 and ops.attention_prefill_wide_usable(D, span, Dv))
+        q = torch.empty((T, Hq * D), dtype=torch.bfloat16 if fast and not self.head_mix else torch.float32, device=dev)
         ops.qk_prepare_store(proj, 0, Hq * D, (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
                              self.k_norm, self.qk_norm_eps or 0.0, pos.inv_freq(), pos.rotary_dim,
                              pos.pairing == "interleaved", pos.amplitude, q, cache.k, cache.v, Hq, Hkv, D, Dv,
                              cache.write, ctx.err, v_inv_freq=vp.inv_freq() if vp is not None else None,
                              v_rot_dim=vp.rotary_dim if vp is not None else 0)
-        span = 1
         if self.head_mix:
-            span = Hkv
-            mixed = torch.empty((T, Hq * Hkv * D), dtype=torch.float32, device=dev)
+            mixed = torch.empty((T, Hq * Hkv * D), dtype=torch.bfloat16 if fast else torch.float32, device=dev)
             ops.mix_query_heads(q, self.mix_weight, mixed, Hq, Hkv, D)
             q = mixed
         turned = vp is not None and vp.rotary_dim > 0
         att = torch.empty((T, Hq * Dv), dtype=torch.float32 if turned else ctx.act_dtype, device=dev)
-        ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
-                                    att, Hq, Hkv, D, Dv, sink_score=self.sink_score, sinks=self.sinks,
-                                    keep_first=self.keep_first, key_span=span)
+        if fast:
+            tiles = batch.T // ops.attention_prefill_wide_tile_rows() + batch.S
+            ops.attention_prefill_wide(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
+                                       self.window, att, Hq, Hkv, D, Dv, keep_first=self.keep_first, sinks=self.sinks,
+                                       key_span=span)
+        else:
+            ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
+                                        self.window, att, Hq, Hkv, D, Dv, sink_score=self.sink_score, sinks=self.sinks,
+                                        keep_first=self.keep_first, key_span=span)
         if turned:
             back = torch.empty((T, Hq * Dv), dtype=ctx.act_dtype, device=dev)
             ops.rotate_heads(att, batch.positions, vp.inv_freq(), vp.rotary_dim, -1.0, back, Hq, Dv)

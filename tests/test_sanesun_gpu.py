@@ -274,7 +274,9 @@ WINDOWS = [ps.attention_layer(heads=4, kv_heads=2, dim=32, vdim=48, window=24, k
            ps.attention_layer(heads=6, kv_heads=1, dim=16, vdim=32, window=500, keep_first=0, rot_dims=16, base=20.0, scale=0.25),
            ps.attention_layer(heads=8, kv_heads=4, dim=64, vdim=64, window=16, keep_first=16, rot_dims=32, base=1e5, scale=0.125),
            ps.attention_layer(heads=2, kv_heads=2, dim=128, vdim=136, window=33, keep_first=2, rot_dims=64, base=3000.0, scale=0.09),
-           ps.attention_layer(heads=5, kv_heads=5, dim=24, vdim=24, window=30, keep_first=40, rot_dims=8, base=50.0, scale=0.2)]
+           ps.attention_layer(heads=5, kv_heads=5, dim=24, vdim=24, window=30, keep_first=40, rot_dims=8, base=50.0, scale=0.2),
+           ps.attention_layer(heads=4, kv_heads=4, dim=96, vdim=80, window=40, keep_first=2, rot_dims=32, base=1e4, scale=0.1),
+           ps.attention_layer(heads=8, kv_heads=2, dim=128, vdim=192, window=20, keep_first=50, rot_dims=128, base=1e6, scale=0.09)]
 
 
 @pytest.mark.parametrize("fast", [True, False])
