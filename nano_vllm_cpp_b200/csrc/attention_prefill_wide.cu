@@ -18,8 +18,15 @@
 //
 // grid = (row tiles, query heads); a CTA takes BM consecutive rows of one request and one query head, each warp 16
 // rows; keys and values come page by page into shared memory in tiles of BN keys with cp.async, double-buffered.
+//
+// The NARROW form is for entries of at most 16 rows (decoded tokens above all): a CTA takes one such entry and one
+// query head, all its warps work on the same 16 rows, and each warp takes 16 of a tile's BN keys with a running
+// maximum, sum and output of its own; the warps' results are merged through shared memory at the end.  With
+// grid.z > 1 the CTAs of one entry and head share out the key tiles, write (output, maximum, sum) per share to a
+// scratch array, and `wide_combine_kernel` merges the shares, adds the sink and writes the rows.
 #include "common.cuh"
 
+#include <limits.h>
 #include <stdlib.h>
 
 namespace {
@@ -33,9 +40,10 @@ struct WideArgs {
   const int* entry_pos0;    // [S]
   const float* sinks;       // [Hq] or null
   void* out;                // [T, Hq, Dv] bfloat16 or float32
+  float* parts;             // NARROW with grid.z > 1: [T, Hq, grid.z, Dv + 2] (output, maximum, sum)
   float scale_log2;         // scale * log2(e)
   int out_f32;
-  int S, max_blocks, window, keep_first, Hq, Hk, Hv, D, KS, Dv, page, min_rows;
+  int S, max_blocks, window, keep_first, Hq, Hk, Hv, D, KS, Dv, page, min_rows, max_rows;
 };
 
 __device__ __forceinline__ uint32_t sm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -67,13 +75,16 @@ __device__ __forceinline__ uint32_t two_bf16(float lo, float hi) {
 constexpr int WIDE_TERMS = 3;
 
 // KDP: key length (KS * D) rounded up to 64, 128, 256 or 512; DVP: value length rounded up to 64, 128 or 256.
-template <int KDP, int DVP, int BM, int BN>
+template <int KDP, int DVP, int BM, int BN, bool NARROW>
 __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideArgs a) {
   constexpr int THREADS = BM * 2;
+  constexpr int QR = NARROW ? 16 : BM;             // query rows of a CTA
+  constexpr int NSUB = NARROW ? 1 : BN / 16;       // blocks of 16 keys that a warp takes of a tile
+  static_assert(!NARROW || BM == BN, "narrow form: one block of 16 keys per warp");
   constexpr int LDK = KDP + 8, LDV = DVP + 8;      // row strides (elements): 16 bytes of padding against bank conflicts
   extern __shared__ __align__(16) uint8_t wide_smem[];
   bf16* Qs = (bf16*)wide_smem;                     // [BM][LDK]
-  bf16* Ks = Qs + BM * LDK;                        // [2][BN][LDK]
+  bf16* Ks = Qs + QR * LDK;                        // [2][BN][LDK]
   bf16* Vs = Ks + 2 * BN * LDK;                    // [2][BN][LDV]
   __shared__ int tile_info[3];                     // entry, first row (batch), rows
 
@@ -88,14 +99,14 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
     int left = (int)(gridDim.x - 1 - blockIdx.x), e = 0, found = -1;
     for (; e < a.S; ++e) {
       const int n = a.cu_rows[e + 1] - a.cu_rows[e];
-      const int tiles = n >= a.min_rows ? (n + BM - 1) / BM : 0;
+      const int tiles = n >= a.min_rows && n <= a.max_rows ? (n + QR - 1) / QR : 0;
       if (left < tiles) { found = e; break; }
       left -= tiles;
     }
     tile_info[0] = found;
     if (found >= 0) {
-      tile_info[1] = a.cu_rows[found] + left * BM;
-      tile_info[2] = min(BM, a.cu_rows[found + 1] - tile_info[1]);
+      tile_info[1] = a.cu_rows[found] + left * QR;
+      tile_info[2] = min(QR, a.cu_rows[found + 1] - tile_info[1]);
     }
   }
   __syncthreads();
@@ -110,63 +121,68 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
   const int endA = min(keep, kv0);                               // kept positions before the window's run
   const int nA = (endA + BN - 1) / BN, nB = (hi - kv0 + BN - 1) / BN;
   const int n_tiles = nA + nB;
+  // this CTA's share of the key tiles (all of them unless the narrow form runs with grid.z > 1)
+  const int t_first = (int)((long long)n_tiles * blockIdx.z / gridDim.z);
+  const int t_end = (int)((long long)n_tiles * (blockIdx.z + 1) / gridDim.z);
   const int* bt = a.block_table + (size_t)e * a.max_blocks;
 
   // ---- Q tile -> shared memory (rows beyond nrows are zero)
   {
     const int qchunks = KD / 8;
-    for (int c = tid; c < BM * qchunks; c += THREADS) {
+    for (int c = tid; c < QR * qchunks; c += THREADS) {
       const int r = c / qchunks, ch = c - r * qchunks;
       bf16* dst = Qs + r * LDK + ch * 8;
       if (r < nrows) copy16(dst, a.q + ((size_t)(row0 + r) * a.Hq + h) * KD + ch * 8);
       else *(uint4*)dst = make_uint4(0, 0, 0, 0);
     }
   }
+  // Eight neighbouring threads bring one key position: its keys (of KS kv heads) and its value, 16 bytes a copy; the
+  // page and the place in it are looked up once per position.
   auto load_kv = [&](int tile, int buf) {
     const int j0 = tile < nA ? tile * BN : kv0 + (tile - nA) * BN;
     const int jend = tile < nA ? endA : hi;
     bf16* kd = Ks + buf * BN * LDK;
     bf16* vd = Vs + buf * BN * LDV;
-    const int per_row = a.KS * kchunks + vchunks;
-    for (int c = tid; c < BN * per_row; c += THREADS) {
-      const int r = c / per_row, w = c - r * per_row;
+    constexpr int LPR = 8;
+    const int sub = tid % LPR;
+    for (int r = tid / LPR; r < BN; r += THREADS / LPR) {
       const int j = j0 + r;
-      int blk = -1, slot = 0;
+      bf16* krow = kd + r * LDK;
+      bf16* vrow = vd + r * LDV;
       if (j < jend) {
-        const int pg = j / a.page;
-        slot = j - pg * a.page;
-        blk = bt[pg];
-      }
-      if (w < a.KS * kchunks) {
-        const int kc_i = w / kchunks, ch = w - kc_i * kchunks;
-        bf16* dst = kd + r * LDK + kc_i * D + ch * 8;
-        if (blk >= 0) copy16(dst, a.kc + (((size_t)blk * a.Hk + kh0 + kc_i) * a.page + slot) * D + ch * 8);
-        else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+        const int pg = j / a.page, slot = j - pg * a.page;
+        const size_t blk = (size_t)bt[pg];
+        for (int kc_i = 0; kc_i < a.KS; ++kc_i) {
+          const bf16* src = a.kc + ((blk * a.Hk + kh0 + kc_i) * a.page + slot) * D;
+          for (int ch = sub; ch < kchunks; ch += LPR) copy16(krow + kc_i * D + ch * 8, src + ch * 8);
+        }
+        const bf16* src = a.vc + ((blk * a.Hv + vh) * a.page + slot) * Dv;
+        for (int ch = sub; ch < vchunks; ch += LPR) copy16(vrow + ch * 8, src + ch * 8);
       } else {
-        const int ch = w - a.KS * kchunks;
-        bf16* dst = vd + r * LDV + ch * 8;
-        if (blk >= 0) copy16(dst, a.vc + (((size_t)blk * a.Hv + vh) * a.page + slot) * Dv + ch * 8);
-        else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+        for (int ch = sub; ch < a.KS * kchunks; ch += LPR) *(uint4*)(krow + ch * 8) = make_uint4(0, 0, 0, 0);
+        for (int ch = sub; ch < vchunks; ch += LPR) *(uint4*)(vrow + ch * 8) = make_uint4(0, 0, 0, 0);
       }
     }
   };
-  load_kv(0, 0);
+  if (t_first < t_end) load_kv(t_first, 0);
   copy_commit();
 
   const int g = lane / 4, tq = lane % 4;
-  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;               // this thread's two rows in the tile
+  const int rw = NARROW ? 0 : warp;                              // which 16 rows of the tile this warp takes
+  const int np0 = NARROW ? warp : 0;                             // and its first block of 16 keys in a key tile
+  const int r_lo = rw * 16 + g, r_hi = r_lo + 8;                 // this thread's two rows in the tile
   const int p_lo = pos0 + r_lo, p_hi = pos0 + r_hi;
   const bool live_lo = r_lo < nrows, live_hi = r_hi < nrows;
-  const int warp_p_lo = pos0 + warp * 16, warp_p_hi = warp_p_lo + 15;
+  const int warp_p_lo = pos0 + rw * 16, warp_p_hi = warp_p_lo + 15;
 
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float o[DVP / 8][4];
 #pragma unroll
   for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  for (int t = 0; t < n_tiles; ++t) {
-    const int buf = t & 1;
-    if (t + 1 < n_tiles) load_kv(t + 1, buf ^ 1);
+  for (int t = t_first; t < t_end; ++t) {
+    const int buf = (t - t_first) & 1;
+    if (t + 1 < t_end) load_kv(t + 1, buf ^ 1);
     copy_commit();
     copy_wait<1>();                                 // tile t (and Q) have landed
     __syncthreads();
@@ -177,36 +193,38 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
     const int jend = kept_run ? endA : hi;
 
     // a warp none of whose rows sees any of the tile's keys only keeps the barriers
-    const bool behind = !kept_run && a.window > 0 && j0 + BN - 1 <= warp_p_lo - a.window && j0 >= keep;
-    const bool warp_sees = warp * 16 < nrows && j0 <= warp_p_hi && !behind;
+    constexpr int KW = NSUB * 16;                   // keys of the tile that this warp takes, from jb0
+    const int jb0 = j0 + np0 * 16;
+    const bool behind = !kept_run && a.window > 0 && jb0 + KW - 1 <= warp_p_lo - a.window && jb0 >= keep;
+    const bool warp_sees = rw * 16 < nrows && jb0 <= warp_p_hi && jb0 < jend && !behind;
     if (warp_sees) {
-      // ---- S = Q K^T for this warp's 16 rows x BN keys
-      float s[BN / 8][4];
+      // ---- S = Q K^T for this warp's 16 rows x KW keys
+      float s[KW / 8][4];
 #pragma unroll
-      for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int i = 0; i < KW / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll 4
       for (int kk = 0; kk < KDP / 16; ++kk) {
         if (kk * 16 < KD) {
           uint32_t qa[4];
-          ldm4(sm_u32(Qs + (warp * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDK + kk * 16 + 8 * (lane / 16)), qa);
+          ldm4(sm_u32(Qs + (rw * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDK + kk * 16 + 8 * (lane / 16)), qa);
 #pragma unroll
-          for (int np = 0; np < BN / 16; ++np) {
+          for (int np = 0; np < NSUB; ++np) {
             uint32_t kf[4];
-            ldm4(sm_u32(kb + (np * 16 + (lane % 8) + 8 * (lane / 16)) * LDK + kk * 16 + 8 * ((lane / 8) % 2)), kf);
+            ldm4(sm_u32(kb + ((np0 + np) * 16 + (lane % 8) + 8 * (lane / 16)) * LDK + kk * 16 + 8 * ((lane / 8) % 2)), kf);
             mma_bf16(s[2 * np], qa, kf[0], kf[1]);
             mma_bf16(s[2 * np + 1], qa, kf[2], kf[3]);
           }
         }
       }
       // ---- mask (unless every row of the warp sees the whole tile), online softmax
-      const bool whole = warp * 16 + 15 < nrows && j0 + BN <= jend && j0 + BN - 1 <= warp_p_lo &&
-                         (a.window <= 0 || j0 > warp_p_hi - a.window || j0 + BN <= keep);
+      const bool whole = rw * 16 + 15 < nrows && jb0 + KW <= jend && jb0 + KW - 1 <= warp_p_lo &&
+                         (a.window <= 0 || jb0 > warp_p_hi - a.window || jb0 + KW <= keep);
       if (!whole) {
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; ++nt) {
+        for (int nt = 0; nt < KW / 8; ++nt) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            const int j = j0 + nt * 8 + 2 * tq + c;
+            const int j = jb0 + nt * 8 + 2 * tq + c;
             const bool in = j < jend;
             const bool see_lo = in && live_lo && j <= p_lo && (a.window <= 0 || j > p_lo - a.window || j < keep);
             const bool see_hi = in && live_hi && j <= p_hi && (a.window <= 0 || j > p_hi - a.window || j < keep);
@@ -217,7 +235,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
       }
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < BN / 8; ++nt) {
+      for (int nt = 0; nt < KW / 8; ++nt) {
         mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
         mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
       }
@@ -234,7 +252,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
       m_hi = mn_hi;
       float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
-      for (int nt = 0; nt < BN / 8; ++nt) {
+      for (int nt = 0; nt < KW / 8; ++nt) {
         s[nt][0] = exp2f(s[nt][0] * a.scale_log2 - ms_lo);
         s[nt][1] = exp2f(s[nt][1] * a.scale_log2 - ms_lo);
         s[nt][2] = exp2f(s[nt][2] * a.scale_log2 - ms_hi);
@@ -250,7 +268,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
       }
       // ---- O += P V, the weights as three bfloat16 terms
 #pragma unroll
-      for (int kb16 = 0; kb16 < BN / 16; ++kb16) {
+      for (int kb16 = 0; kb16 < NSUB; ++kb16) {
         uint32_t pt[WIDE_TERMS][4];
         {
           float w[8] = {s[2 * kb16][0], s[2 * kb16][1], s[2 * kb16][2], s[2 * kb16][3],
@@ -272,7 +290,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
         for (int dp = 0; dp < DVP / 16; ++dp) {
           if (dp * 16 < Dv) {
             uint32_t vf[4];
-            ldm4_t(sm_u32(vb + (kb16 * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDV + dp * 16 + 8 * (lane / 16)), vf);
+            ldm4_t(sm_u32(vb + ((np0 + kb16) * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDV + dp * 16 + 8 * (lane / 16)), vf);
 #pragma unroll
             for (int term = 0; term < WIDE_TERMS; ++term) {
               mma_bf16(o[2 * dp], pt[term], vf[0], vf[1]);
@@ -290,6 +308,56 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if constexpr (NARROW) {
+    // ---- the warps' results for the same rows are merged: (output, maximum, sum) per warp and row in shared memory
+    constexpr int NW = BM / 16, PS = DVP + 2;
+    float* mg = (float*)wide_smem;                  // [NW][16][PS]
+    __syncthreads();                                // every thread's copies have landed; nobody reads a tile any more
+    float* my = mg + (size_t)warp * 16 * PS;
+#pragma unroll
+    for (int i = 0; i < DVP / 8; ++i) {
+      const int d = i * 8 + 2 * tq;
+      my[g * PS + d] = o[i][0];
+      my[g * PS + d + 1] = o[i][1];
+      my[(g + 8) * PS + d] = o[i][2];
+      my[(g + 8) * PS + d + 1] = o[i][3];
+    }
+    if (tq == 0) {
+      my[g * PS + DVP] = m_lo;
+      my[g * PS + DVP + 1] = l_lo;
+      my[(g + 8) * PS + DVP] = m_hi;
+      my[(g + 8) * PS + DVP + 1] = l_hi;
+    }
+    __syncthreads();
+    const float sk = a.sinks ? a.sinks[h] * 1.4426950408889634f : 0.f;
+    for (int idx = tid; idx < nrows * Dv; idx += THREADS) {
+      const int r = idx / Dv, d = idx - r * Dv;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) M = fmaxf(M, mg[(w * 16 + r) * PS + DVP]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float* pw = mg + (size_t)(w * 16 + r) * PS;
+        const float f = pw[DVP] == -INFINITY ? 0.f : exp2f((pw[DVP] - M) * a.scale_log2);
+        L += f * pw[DVP + 1];
+        O += f * pw[d];
+      }
+      const size_t row = (size_t)(row0 + r);
+      if (gridDim.z > 1) {
+        float* pp = a.parts + ((row * a.Hq + h) * gridDim.z + blockIdx.z) * (size_t)(Dv + 2);
+        pp[d] = O;
+        if (d == 0) { pp[Dv] = M; pp[Dv + 1] = L; }
+      } else {
+        if (a.sinks) L += exp2f(sk - (M == -INFINITY ? 0.f : M * a.scale_log2));
+        const float v = L > 0.f ? O / L : 0.f;
+        const size_t at = (row * a.Hq + h) * Dv + d;
+        if (a.out_f32) ((float*)a.out)[at] = v;
+        else ((bf16*)a.out)[at] = __float2bfloat16(v);
+      }
+    }
+    return;
+  }
   if (a.sinks) {                                    // relative to the same reference as the sums: exp2(sink - m)
     const float sk = a.sinks[h] * 1.4426950408889634f;
     l_lo += exp2f(sk - (m_lo == -INFINITY ? 0.f : m_lo * a.scale_log2));
@@ -316,25 +384,58 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
   }
 }
 
-template <int KDP, int DVP, int BM, int BN>
-int launch_wide(const WideArgs& a, int max_tiles, cudaStream_t s) {
-  const size_t smem = ((size_t)(BM + 2 * BN) * (KDP + 8) + (size_t)2 * BN * (DVP + 8)) * sizeof(bf16);
+// The shares of the narrow form's key tiles, merged: one CTA per entry and query head.
+__global__ void wide_combine_kernel(WideArgs a, int Z) {
+  const int e = blockIdx.x, h = blockIdx.y, Dv = a.Dv;
+  const int first = a.cu_rows[e], n = a.cu_rows[e + 1] - first;
+  if (n < a.min_rows || n > a.max_rows) return;
+  const float sk = a.sinks ? a.sinks[h] * 1.4426950408889634f : 0.f;
+  for (int idx = threadIdx.x; idx < n * Dv; idx += blockDim.x) {
+    const int r = idx / Dv, d = idx - r * Dv;
+    const size_t row = (size_t)(first + r);
+    const float* pp = a.parts + ((row * a.Hq + h) * Z) * (size_t)(Dv + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < Z; ++z) M = fmaxf(M, pp[(size_t)z * (Dv + 2) + Dv]);
+    float L = 0.f, O = 0.f;
+    for (int z = 0; z < Z; ++z) {
+      const float* pz = pp + (size_t)z * (Dv + 2);
+      const float f = pz[Dv] == -INFINITY ? 0.f : exp2f((pz[Dv] - M) * a.scale_log2);
+      L += f * pz[Dv + 1];
+      O += f * pz[d];
+    }
+    if (a.sinks) L += exp2f(sk - (M == -INFINITY ? 0.f : M * a.scale_log2));
+    const float v = L > 0.f ? O / L : 0.f;
+    const size_t at = (row * a.Hq + h) * Dv + d;
+    if (a.out_f32) ((float*)a.out)[at] = v;
+    else ((bf16*)a.out)[at] = __float2bfloat16(v);
+  }
+}
+
+template <int KDP, int DVP, int BM, int BN, bool NARROW>
+int launch_wide(const WideArgs& a, int max_tiles, int splits, cudaStream_t s) {
+  const size_t smem = ((size_t)((NARROW ? 16 : BM) + 2 * BN) * (KDP + 8) + (size_t)2 * BN * (DVP + 8)) * sizeof(bf16);
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_wide_kernel<KDP, DVP, BM, BN>,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_wide_kernel<KDP, DVP, BM, BN, NARROW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  attention_prefill_wide_kernel<KDP, DVP, BM, BN><<<dim3(max_tiles, a.Hq), BM * 2, smem, s>>>(a);
+  const int Z = NARROW ? splits : 1;
+  attention_prefill_wide_kernel<KDP, DVP, BM, BN, NARROW><<<dim3(max_tiles, a.Hq, Z), BM * 2, smem, s>>>(a);
+  if (Z > 1) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    wide_combine_kernel<<<dim3(a.S, a.Hq), 128, 0, s>>>(a, Z);
+  }
   NV_RETURN_LAST();
 }
 
-template <int KDP, int BM, int BN>
-int launch_wide_v(const WideArgs& a, int max_tiles, cudaStream_t s) {
-  if (a.Dv <= 64) return launch_wide<KDP, 64, BM, BN>(a, max_tiles, s);
-  if (a.Dv <= 128) return launch_wide<KDP, 128, BM, BN>(a, max_tiles, s);
-  return launch_wide<KDP, 256, BM, BN>(a, max_tiles, s);
+template <int KDP, int BM, int BN, bool NARROW>
+int launch_wide_v(const WideArgs& a, int max_tiles, int splits, cudaStream_t s) {
+  if (a.Dv <= 64) return launch_wide<KDP, 64, BM, BN, NARROW>(a, max_tiles, splits, s);
+  if (a.Dv <= 128) return launch_wide<KDP, 128, BM, BN, NARROW>(a, max_tiles, splits, s);
+  return launch_wide<KDP, 256, BM, BN, NARROW>(a, max_tiles, splits, s);
 }
 
 }  // namespace
@@ -352,21 +453,34 @@ NV_API int nv_attention_prefill_wide(const void* q, const void* kc, const void* 
                                      int max_blocks, const int* cu_rows, const int* entry_pos0, int S, int max_tiles,
                                      float scale, int window, int keep_first, const float* sinks, void* out,
                                      int out_f32, int Hq, int Hk, int Hv, int D, int KS, int Dv, int page, int min_rows,
-                                     cudaStream_t stream) {
+                                     int max_rows, int narrow, int splits, float* parts, cudaStream_t stream) {
   if (!nv_attention_prefill_wide_usable(D, KS, Dv) || !(scale > 0.f)) return NV_ERR_UNSUPPORTED;
   if (Hq <= 0 || Hk <= 0 || Hv <= 0 || Hq % Hv || (KS == 1 ? Hq % Hk : KS != Hk) || keep_first < 0 || page <= 0)
     return NV_ERR_BAD_SIZE;
   if (((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)out & 7)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0) return NV_OK;
+  if (max_rows <= 0) max_rows = INT_MAX;
+  if (narrow) {
+    if (max_rows > 16) max_rows = 16;               // one tile of 16 rows per entry
+    if (splits < 1) splits = 1;
+    if (splits > 1 && !parts) return NV_ERR_BAD_SIZE;
+    if (max_tiles < S) return NV_ERR_BAD_SIZE;
+  }
   WideArgs a;
   a.q = (const bf16*)q; a.kc = (const bf16*)kc; a.vc = (const bf16*)vc; a.block_table = block_table;
   a.cu_rows = cu_rows; a.entry_pos0 = entry_pos0; a.sinks = sinks;
   a.out = out; a.scale_log2 = scale * 1.4426950408889634f; a.out_f32 = out_f32;
   a.S = S; a.max_blocks = max_blocks; a.window = window; a.keep_first = keep_first; a.Hq = Hq; a.Hk = Hk; a.Hv = Hv;
-  a.D = D; a.KS = KS; a.Dv = Dv; a.page = page; a.min_rows = min_rows;
+  a.D = D; a.KS = KS; a.Dv = Dv; a.page = page; a.min_rows = min_rows; a.max_rows = max_rows; a.parts = parts;
   const int KD = D * KS;
-  if (KD <= 64) return launch_wide_v<64, 128, 64>(a, max_tiles, stream);
-  if (KD <= 128) return launch_wide_v<128, 128, 64>(a, max_tiles, stream);
-  if (KD <= 256) return launch_wide_v<256, 128, 64>(a, max_tiles, stream);
-  return launch_wide_v<512, 64, 32>(a, max_tiles, stream);
+  if (narrow) {
+    if (KD <= 64) return launch_wide_v<64, 64, 64, true>(a, S, splits, stream);
+    if (KD <= 128) return launch_wide_v<128, 64, 64, true>(a, S, splits, stream);
+    if (KD <= 256) return launch_wide_v<256, 64, 64, true>(a, S, splits, stream);
+    return launch_wide_v<512, 32, 32, true>(a, S, splits, stream);
+  }
+  if (KD <= 64) return launch_wide_v<64, 128, 64, false>(a, max_tiles, 1, stream);
+  if (KD <= 128) return launch_wide_v<128, 128, 64, false>(a, max_tiles, 1, stream);
+  if (KD <= 256) return launch_wide_v<256, 128, 64, false>(a, max_tiles, 1, stream);
+  return launch_wide_v<512, 64, 32, false>(a, max_tiles, 1, stream);
 }

@@ -295,6 +295,26 @@ def test_window_attention_alone(dtype, layer, fast):
         close(got[i], ps.window_attention(x, W, "m.", layer["mixer"]), PART_TOL[dtype], f"request {i}")
 
 
+@pytest.mark.parametrize("layer", [ps.attention_layer(heads=4, kv_heads=2, dim=32, vdim=48, window=300, keep_first=5, rot_dims=16, base=500.0, scale=0.2),
+                                   ps.attention_layer(heads=2, kv_heads=1, dim=64, vdim=32, window=90, keep_first=70, rot_dims=32, base=1e4, scale=0.15),
+                                   ps.attention_layer(heads=3, kv_heads=3, dim=128, vdim=144, window=1000, keep_first=0, rot_dims=0, base=50.0, scale=0.1)])
+def test_short_entries_far_into_a_sequence(layer):
+    """Single rows and portions of 2 to 16 rows hundreds of positions into a sequence, beside a longer portion of
+    another request: in a bfloat16 run the short entries' keys are shared out among warps and blocks and merged."""
+    width = 80
+    W = ps.mixer_weights(layer, width, 41)
+    part, cache, ctx = mixer_setup(layer, width, W, torch.bfloat16, True, pages=64)
+    xs = inputs(width, [700, 120], 42)
+    g = torch.Generator().manual_seed(5)
+    order = torch.randperm(60, generator=g).tolist()
+    tables = [order[:44], order[44:52]]
+    cuts = [[(0, 640), None], [(640, 641), None], [(641, 642), (0, 70)], [(642, 658), (70, 71)], [(658, 660), (71, 72)],
+            [(660, 669), (72, 88)], [(669, 670), (88, 120)], [(670, 700), None]]
+    got = run_cut(part, cache, xs, cuts, torch.bfloat16, tables, ctx)
+    for i, x in enumerate(xs):
+        close(got[i], ps.window_attention(x, W, "m.", layer["mixer"]), PART_TOL[torch.bfloat16], f"request {i}")
+
+
 def edge_case(window, keep, T, i, j, width=64):
     """Weights and inputs for which row i's softmax weight falls on key j and on itself, if it sees j: the q heads
     are copies of the one k head (nothing of them is turned, no biases), row i's input is large, row j's is the same
