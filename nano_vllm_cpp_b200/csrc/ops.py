@@ -470,12 +470,20 @@ def attention_prefill_wide_tile_rows() -> int:
 
 def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
                            window: int, out, Hq: int, Hkv: int, D: int, Dv: int, *, keep_first: int = 0, sinks=None,
-                           key_span: int = 1, min_rows: int = 1) -> None:
+                           key_span: int = 1, min_rows: int = 1, max_rows: int = 0, narrow: bool = False,
+                           max_keys: int = 0) -> None:
     """bfloat16 rows of any mix of portions (single rows too) against paged keys of ``D`` and values of ``Dv``
     elements, on the tensor cores with float32 softmax weights (three bfloat16 terms).  ``q`` [T, Hq * key_span * D]:
     with ``key_span`` = Hkv > 1 a query head is scored against all kv heads' keys side by side (queries mixed across
     heads).  ``keep_first``: the first so many positions stay visible behind the window; ``sinks`` [Hq] float32: a
-    learned score without key and value in every softmax.  ``out`` [T, Hq * Dv] bfloat16 or float32."""
+    learned score without key and value in every softmax.  ``out`` [T, Hq * Dv] bfloat16 or float32.  Entries with
+    fewer than ``min_rows`` or (``max_rows`` > 0) more than ``max_rows`` rows are skipped and their rows of ``out``
+    left as they are.
+
+    ``narrow``: the form for entries of at most ``attention_wide_narrow_rows()`` rows, decoded tokens above all (it
+    skips longer entries): all warps of a CTA work on the entry's rows and share out the keys, and when the step has
+    too few entries and heads to fill the multiprocessors, several CTAs share out the key tiles of one entry and head
+    and a second kernel merges them (``max_keys``: the most keys any such entry reads, which bounds the shares)."""
     _cuda_contig(q, k_cache, v_cache, block_table, cu_rows, entry_pos0, out, sinks)
     _i32(block_table, cu_rows, entry_pos0)
     _f32(sinks)
@@ -487,11 +495,26 @@ def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0
     _need(k_cache.shape[1] == Hkv and k_cache.shape[3] == D and v_cache.shape[3] == Dv and key_span in (1, Hkv),
           "attention_prefill_wide: cache shapes")
     _need(sinks is None or sinks.numel() == Hq, "attention_prefill_wide: one sink per head")
+    S = entry_pos0.numel()
+    splits, parts = 1, None
+    if narrow:
+        max_tiles = S
+        ctas = max(1, S * Hq)
+        key_tiles = max(1, (max(1, max_keys) + 63) // 64)
+        splits = max(1, min(32, key_tiles, (2 * num_sms() + ctas - 1) // ctas))
+        if splits > 1:
+            parts = torch.empty(T * Hq * splits * (Dv + 2), dtype=torch.float32, device=q.device)
     _check(lib().nv_attention_prefill_wide(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
-                                           _p(cu_rows), _p(entry_pos0), entry_pos0.numel(), max_tiles, scale, window,
+                                           _p(cu_rows), _p(entry_pos0), S, max_tiles, scale, window,
                                            keep_first, _p(sinks), _p(out), (1 if out.dtype == torch.float32 else 0), Hq,
                                            Hkv, v_cache.shape[1], D, key_span, Dv, k_cache.shape[2], min_rows,
-                                           _stream()), "attention_prefill_wide")
+                                           max_rows, (1 if narrow else 0), splits, _p(parts), _stream()),
+           "attention_prefill_wide")
+
+
+def attention_wide_narrow_rows() -> int:
+    """The most rows of an entry that the narrow form of ``attention_prefill_wide`` takes."""
+    return 16
 
 
 def gemm_plain_tile_m() -> int:
@@ -1072,6 +1095,18 @@ def head_project(x, w, out, H: int, K: int, N: int, gate=None, gate_col: int = 0
 
 # ----------------------------------------------------------------------------- fast products
 _num_sms = None
+
+
+def head_gate(x, gate, gate_col: int, out, H: int, N: int) -> None:
+    """``out[t, h, :] = x[t, h, :] * sigmoid(gate[t, gate_col + h])`` for float32 ``x`` [T, H * N] and float32 ``gate``
+    rows; ``out`` in either dtype."""
+    _cuda_contig(x, out)
+    _f32(x, gate)
+    T = x.shape[0]
+    _need(x.shape == (T, H * N) and out.shape == x.shape and gate.stride(-1) == 1 and gate.shape[0] == T
+          and gate.shape[1] >= gate_col + H, "head_gate: shapes")
+    _check(lib().nv_head_gate(_p(x), _p(gate), gate.stride(0), gate_col, _p(out), dt(out), T, H, N, _stream()),
+           "head_gate")
 
 
 def stream_mix_norm(x, streams: int, *, branch=None, mix=None, carry=None, write=None, read=None, norm=None,

@@ -712,6 +712,65 @@ __global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const void* __
   }
 }
 
+// out[t, h, :] = x[t, h, :] * sigmoid(gate[t, gate0 + h]): the gate alone, for head outputs that another product made.
+__global__ void head_gate_kernel(const float* __restrict__ x, const float* __restrict__ gate, long long gate_ld, int gate0,
+                                 void* __restrict__ out, int out_dt, long long total, int H, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long th = i / N;
+  const long long t = th / H;
+  const int h = (int)(th - t * H);
+  st_dt(out, out_dt, (size_t)i, x[i] * sigmoidf_(gate[t * gate_ld + gate0 + h]));
+}
+
+// The same for few rows (a decode step): a block takes HP_ROWS rows, one head and 32 output columns, its four warps
+// share out k in quarters (each sums its quarter in ascending order, several loads in flight) and the quarters are
+// added in ascending order through shared memory.
+constexpr int HP_FEW_COLS = 32;
+
+__global__ void __launch_bounds__(HP_THREADS) head_project_few_kernel(const void* __restrict__ x, int x_dt,
+                                                                      const void* __restrict__ w, int w_dt,
+                                                                      const float* __restrict__ gate, long long gate_ld,
+                                                                      int gate0, void* __restrict__ out, int out_dt, int T,
+                                                                      int H, int K, int N) {
+  extern __shared__ float xs[];      // HP_ROWS * K, then [4][HP_ROWS][HP_FEW_COLS] partial sums
+  float* part = xs + (size_t)HP_ROWS * K;
+  const int t0 = blockIdx.x * HP_ROWS, h = blockIdx.y;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n = blockIdx.z * HP_FEW_COLS + lane;
+  const int rows = min(HP_ROWS, T - t0);
+  for (int i = threadIdx.x; i < HP_ROWS * K; i += HP_THREADS) {
+    const int r = i / K, k = i % K;
+    xs[i] = r < rows ? ld_dt(x, x_dt, ((size_t)(t0 + r) * H + h) * K + k) : 0.f;
+  }
+  __syncthreads();
+  float acc[HP_ROWS];
+#pragma unroll
+  for (int r = 0; r < HP_ROWS; ++r) acc[r] = 0.f;
+  if (n < N) {
+    const int kq = (K + 3) / 4, k0 = warp * kq, k1 = min(K, k0 + kq);
+#pragma unroll 8
+    for (int k = k0; k < k1; ++k) {
+      const float wv = ld_dt(w, w_dt, ((size_t)h * K + k) * N + n);
+#pragma unroll
+      for (int r = 0; r < HP_ROWS; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < HP_ROWS; ++r) part[(warp * HP_ROWS + r) * HP_FEW_COLS + lane] = acc[r];
+  __syncthreads();
+  for (int i = threadIdx.x; i < HP_ROWS * HP_FEW_COLS; i += HP_THREADS) {
+    const int r = i / HP_FEW_COLS, c = i % HP_FEW_COLS, nn = blockIdx.z * HP_FEW_COLS + c;
+    if (r < rows && nn < N) {
+      float sum = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) sum += part[(q * HP_ROWS + r) * HP_FEW_COLS + c];
+      const float g = gate ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + h]) : 1.f;
+      st_dt(out, out_dt, ((size_t)(t0 + r) * H + h) * N + nn, sum * g);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ the same memories, a column per thread
 // A column of the head's matrix (its dk rows) stays in one thread's registers while the entry's rows run: the
 // columns of either recurrence never meet, so a row costs one barrier (for q and k of the row, staged in shared
@@ -1296,11 +1355,29 @@ NV_API int nv_head_project(const void* x, int x_dt, const void* w, int w_dt, con
   if (!dt_ok(x_dt) || !dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (H <= 0 || K <= 0 || N <= 0) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
+  if (T <= 8 * HP_ROWS) {            // few rows: more blocks, each with a shorter chain of sums
+    const size_t few = sizeof(float) * ((size_t)HP_ROWS * K + 4 * HP_ROWS * HP_FEW_COLS);
+    int rc = allow_smem(head_project_few_kernel, few);
+    if (rc) return rc;
+    head_project_few_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H, (N + HP_FEW_COLS - 1) / HP_FEW_COLS), HP_THREADS, few, s>>>(
+        x, x_dt, w, w_dt, gate, gate_ld, gate0, out, out_dt, T, H, K, N);
+    NV_RETURN_LAST();
+  }
   const size_t smem = sizeof(float) * (size_t)HP_ROWS * K;
   int rc = allow_smem(head_project_kernel, smem);
   if (rc) return rc;
   head_project_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H), HP_THREADS, smem, s>>>(x, x_dt, w, w_dt, gate, gate_ld, gate0,
                                                                                      out, out_dt, T, H, K, N);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_head_gate(const float* x, const float* gate, long long gate_ld, int gate0, void* out, int out_dt, int T,
+                        int H, int N, cudaStream_t s) {
+  if (!dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (H <= 0 || N <= 0) return NV_ERR_BAD_SIZE;
+  if (T == 0) return NV_OK;
+  const long long total = (long long)T * H * N;
+  head_gate_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, gate, gate_ld, gate0, out, out_dt, total, H, N);
   NV_RETURN_LAST();
 }
 

@@ -25,6 +25,8 @@ class LatentAttention(Mixer):
     page pool therefore holds one array of ``kv_rank`` elements per token and layer.  ``output_gate`` False leaves
     the sigmoid gate out.  ``names`` renames the tensors (keys: dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o)."""
 
+    TC_HEADS_MIN_ROWS = 64      # steps of more rows make the per-head products on the tensor cores (bfloat16 runs)
+
     _NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
               "uv": "uv", "g": "g", "o": "o"}
 
@@ -60,6 +62,13 @@ class LatentAttention(Mixer):
         self.w_uk = fetch(n["uk"]).view(H, D, rk).contiguous()                       # [h][d][r]: q_h -> W_uk[h]^T q_h
         self.w_uv = fetch(n["uv"]).view(H, Dv, rk).transpose(1, 2).contiguous()      # [h][r][v]: latent sum -> o_h
         self.w_out = fetch(n["o"])
+        # A bfloat16 run with many rows makes the two small products per head on the tensor cores, head by head
+        # on views of the rows: the weights as [out, in] per head.
+        self.tc_heads = (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and self.w_uk.dtype == torch.bfloat16
+                         and D % 8 == 0 and Dv % 8 == 0 and rk % 8 == 0)
+        if self.tc_heads:
+            self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()                     # [h][r][d]
+            self.w_uv_n = fetch(n["uv"]).view(H, Dv, rk).contiguous()                # [h][v][r]
 
     def cache_spec(self):
         return KVCacheSpec(1, self.rk, 0, 0, 0, values=False)
@@ -75,7 +84,6 @@ class LatentAttention(Mixer):
         # the queries: norm of the latent, up, and over to c's space
         cq = torch.empty((T, rq), dtype=ctx.act_dtype, device=dev)
         ops.cols_rmsnorm(down, 0, rq, self.dq_norm, self.eps, cq)
-        q = linear(ctx, cq, self.w_uq, torch.float32)
         # A bfloat16 run whose latent is a head size of the tensor-core kernels attends through them: one shared
         # "kv head" of kv_rank elements whose pages are keys and values at once (single rows through the split-key
         # decode kernel, the others through the prompt kernel; the softmax weights keep their float32 bits in the
@@ -83,8 +91,15 @@ class LatentAttention(Mixer):
         fast = (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
                 and rk % 16 == 0 and rk <= 256)
         mid = torch.bfloat16 if fast else torch.float32
+        tc = fast and self.tc_heads and T > self.TC_HEADS_MIN_ROWS
         q_lat = torch.empty((T, H * rk), dtype=mid, device=dev)
-        ops.head_project(q, self.w_uk, q_lat, H, D, rk)
+        if tc:
+            q = linear(ctx, cq, self.w_uq, torch.bfloat16)
+            for h in range(H):
+                linear(ctx, q[:, h * D:(h + 1) * D], self.w_uk_t[h], mid, out=q_lat[:, h * rk:(h + 1) * rk])
+        else:
+            q = linear(ctx, cq, self.w_uq, torch.float32)
+            ops.head_project(q, self.w_uk, q_lat, H, D, rk)
         lat = torch.empty((T, H * rk), dtype=mid, device=dev)
         if fast:
             single = batch.n_single if ops.attention_decode_usable(cache.k, rk) else 0
@@ -101,7 +116,14 @@ class LatentAttention(Mixer):
             ops.paged_attention_general(q_lat, cache.k, None, bt, batch.row_entry, batch.positions, self.scale, 0, lat,
                                         H, 1, rk, rk)
         o = torch.empty((T, H * Dv), dtype=ctx.act_dtype, device=dev)
-        ops.head_project(lat, self.w_uv, o, H, rk, Dv, gate=down if self.output_gate else None, gate_col=rq + rk)
+        if tc:
+            o32 = torch.empty((T, H * Dv), dtype=torch.float32, device=dev) if self.output_gate else o
+            for h in range(H):
+                linear(ctx, lat[:, h * rk:(h + 1) * rk], self.w_uv_n[h], o32.dtype, out=o32[:, h * Dv:(h + 1) * Dv])
+            if self.output_gate:
+                ops.head_gate(o32, down, rq + rk, o, H, Dv)
+        else:
+            ops.head_project(lat, self.w_uv, o, H, rk, Dv, gate=down if self.output_gate else None, gate_col=rq + rk)
         return linear(ctx, o, self.w_out, torch.float32)
 
 

@@ -457,6 +457,23 @@ def test_latent_attention_alone(dtype, layer, fast):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layer", [LATENTS[3], ps.latent_layer(heads=4, dim=40, vdim=56, q_rank=24, kv_rank=48, scale=0.2),
+                                   ps.latent_layer(heads=2, dim=36, vdim=20, q_rank=16, kv_rank=64, scale=0.2)])
+def test_latent_attention_steps_of_many_rows(dtype, layer):
+    """Steps of hundreds of rows, alone and beside single rows: a bfloat16 run makes the per-head products of such
+    steps another way (head by head on the tensor cores where the sizes allow) than those of a few rows."""
+    width, eps = 96, 1e-5
+    W = ps.mixer_weights(layer, width, 45)
+    part, cache, ctx = mixer_setup(layer, width, W, dtype, pages=40, eps=eps)
+    xs = inputs(width, [300, 101], 46)
+    tables = [[(7 * p + 2) % 19 for p in range(19)], list(range(19, 26))]
+    cuts = [[(0, 200), None], [(200, 201), (0, 100)], [(201, 300), (100, 101)]]
+    got = run_cut(part, cache, xs, cuts, dtype, tables, ctx)
+    for i, x in enumerate(xs):
+        close(got[i], ps.latent_attention(x, W, "m.", layer["mixer"], eps), PART_TOL[dtype], f"request {i}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("decoded", [False, True])
 @pytest.mark.parametrize("T,i,j", [(600, 590, 3), (600, 590, 0), (330, 320, 16), (330, 320, 15)])
 def test_latent_attention_reads_a_far_key(T, i, j, decoded, dtype):
