@@ -119,3 +119,36 @@ def test_a_numeric_suffix_marks_a_further_set_of_sizes():
     assert [L.type for L in typed.layers] == ["latent_attention", "channel_delta", "attention", "attention_2",
                                               "channel_delta_2"]
     assert type(typed.layers[2].mixer) is type(typed.layers[3].mixer)
+
+
+@pytest.mark.parametrize("keep", [1, 16, 17, 40])
+def test_pages_of_kept_positions_stay_with_the_request(keep):
+    """A window group gives a page back once the window has passed it, but never a page that holds one of the
+    sequence's first ``keep`` positions; pages come back to the pool at the request's end and are used again."""
+    from nano_vllm_cpp_b200.cache import CacheManager
+    m = CacheManager([(16, keep), 16], [12, 12], 16, max_requests=2)
+    m.open("r")
+    n = 0
+    for step in [5, 30, 1, 1, 40, 1, 2, 64, 1, 1]:
+        m.extend("r", n, n + step)
+        n += step
+        m.commit("r", n)
+        kept, plain = m.get("r").tables
+        first = (min(keep, n) + 15) // 16              # pages that hold a kept position
+        assert all(kept[i] >= 0 for i in range(first)), (n, kept)
+        assert all(kept[i] >= 0 for i in range(max(0, n - 15) // 16, len(kept)))
+        m.check()
+    m.extend("r", n, n + 1)                            # the next row's pages are found: the window's passed pages go back
+    kept, plain = m.get("r").tables
+    first, lo = (keep + 15) // 16, (n - 15) // 16
+    assert [i for i, p in enumerate(kept) if p >= 0] == sorted(set(range(first)) | set(range(lo, len(kept))))
+    assert [i for i, p in enumerate(plain) if p >= 0] == list(range(lo, len(plain)))
+    m.commit("r", n + 1)
+    m.check()
+    held = {p for p in m.get("r").tables[0] if p >= 0}
+    m.close("r")
+    m.open("s")
+    m.extend("s", 0, 16 * 12)                          # the whole pool again, the kept pages among it
+    assert held <= {p for p in m.get("s").tables[0] if p >= 0}
+    m.close("s")
+    m.check()
