@@ -24,6 +24,12 @@
 // maximum, sum and output of its own; the warps' results are merged through shared memory at the end.  With
 // grid.z > 1 the CTAs of one entry and head share out the key tiles, write (output, maximum, sum) per share to a
 // scratch array, and `wide_combine_kernel` merges the shares, adds the sink and writes the rows.
+//
+// The HEADS form is the narrow form for entries of one row whose query heads all read the same keys (KS = Hk: mixed
+// heads, or one kv head) and number at most 16: the 16 rows of a CTA's tile are the row's query heads, so the keys
+// are read once for all heads.  The values of all Hv value heads come with each key tile; the weights of the
+// heads of one value head at a time (the other rows set to zero) are multiplied with that head's values into the
+// same accumulators.
 #include "common.cuh"
 
 #include <limits.h>
@@ -75,8 +81,10 @@ __device__ __forceinline__ uint32_t two_bf16(float lo, float hi) {
 constexpr int WIDE_TERMS = 3;
 
 // KDP: key length (KS * D) rounded up to 64, 128, 256 or 512; DVP: value length rounded up to 64, 128 or 256.
-template <int KDP, int DVP, int BM, int BN, bool NARROW>
+// FORM 0: tiles of BM rows; 1: narrow; 2: heads as rows.
+template <int KDP, int DVP, int BM, int BN, int FORM>
 __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideArgs a) {
+  constexpr bool NARROW = FORM != 0, HEADS = FORM == 2;
   constexpr int THREADS = BM * 2;
   constexpr int QR = NARROW ? 16 : BM;             // query rows of a CTA
   constexpr int NSUB = NARROW ? 1 : BN / 16;       // blocks of 16 keys that a warp takes of a tile
@@ -85,7 +93,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
   extern __shared__ __align__(16) uint8_t wide_smem[];
   bf16* Qs = (bf16*)wide_smem;                     // [BM][LDK]
   bf16* Ks = Qs + QR * LDK;                        // [2][BN][LDK]
-  bf16* Vs = Ks + 2 * BN * LDK;                    // [2][BN][LDV]
+  bf16* Vs = Ks + 2 * BN * LDK;                    // [2][BN][ldv]
   __shared__ int tile_info[3];                     // entry, first row (batch), rows
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -93,6 +101,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
   const int D = a.D, KD = a.KS * a.D, Dv = a.Dv;
   const int kh0 = a.KS > 1 ? 0 : h / (a.Hq / a.Hk);
   const int vh = h / (a.Hq / a.Hv);
+  const int ldv = HEADS ? a.Hv * a.Dv + 8 : LDV;   // the HEADS form keeps every value head's values of a key side by side
   const int kchunks = D / 8, vchunks = Dv / 8;
 
   if (tid == 0) {                                  // which (entry, tile of BM rows) is this CTA's?  Late tiles first.
@@ -132,7 +141,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
     for (int c = tid; c < QR * qchunks; c += THREADS) {
       const int r = c / qchunks, ch = c - r * qchunks;
       bf16* dst = Qs + r * LDK + ch * 8;
-      if (r < nrows) copy16(dst, a.q + ((size_t)(row0 + r) * a.Hq + h) * KD + ch * 8);
+      if (HEADS ? r < a.Hq : r < nrows) copy16(dst, a.q + ((size_t)(row0 + (HEADS ? 0 : r)) * a.Hq + (HEADS ? r : h)) * KD + ch * 8);
       else *(uint4*)dst = make_uint4(0, 0, 0, 0);
     }
   }
@@ -142,13 +151,13 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
     const int j0 = tile < nA ? tile * BN : kv0 + (tile - nA) * BN;
     const int jend = tile < nA ? endA : hi;
     bf16* kd = Ks + buf * BN * LDK;
-    bf16* vd = Vs + buf * BN * LDV;
+    bf16* vd = Vs + buf * BN * ldv;
     constexpr int LPR = 8;
     const int sub = tid % LPR;
     for (int r = tid / LPR; r < BN; r += THREADS / LPR) {
       const int j = j0 + r;
       bf16* krow = kd + r * LDK;
-      bf16* vrow = vd + r * LDV;
+      bf16* vrow = vd + r * ldv;
       if (j < jend) {
         const int pg = j / a.page, slot = j - pg * a.page;
         const size_t blk = (size_t)bt[pg];
@@ -156,11 +165,14 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
           const bf16* src = a.kc + ((blk * a.Hk + kh0 + kc_i) * a.page + slot) * D;
           for (int ch = sub; ch < kchunks; ch += LPR) copy16(krow + kc_i * D + ch * 8, src + ch * 8);
         }
-        const bf16* src = a.vc + ((blk * a.Hv + vh) * a.page + slot) * Dv;
-        for (int ch = sub; ch < vchunks; ch += LPR) copy16(vrow + ch * 8, src + ch * 8);
+        for (int v = HEADS ? 0 : vh; v < (HEADS ? a.Hv : vh + 1); ++v) {
+          const bf16* src = a.vc + ((blk * a.Hv + v) * a.page + slot) * Dv;
+          bf16* dst = vrow + (HEADS ? v * Dv : 0);
+          for (int ch = sub; ch < vchunks; ch += LPR) copy16(dst + ch * 8, src + ch * 8);
+        }
       } else {
         for (int ch = sub; ch < a.KS * kchunks; ch += LPR) *(uint4*)(krow + ch * 8) = make_uint4(0, 0, 0, 0);
-        for (int ch = sub; ch < vchunks; ch += LPR) *(uint4*)(vrow + ch * 8) = make_uint4(0, 0, 0, 0);
+        for (int ch = sub; ch < (HEADS ? a.Hv : 1) * vchunks; ch += LPR) *(uint4*)(vrow + ch * 8) = make_uint4(0, 0, 0, 0);
       }
     }
   };
@@ -171,9 +183,11 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
   const int rw = NARROW ? 0 : warp;                              // which 16 rows of the tile this warp takes
   const int np0 = NARROW ? warp : 0;                             // and its first block of 16 keys in a key tile
   const int r_lo = rw * 16 + g, r_hi = r_lo + 8;                 // this thread's two rows in the tile
-  const int p_lo = pos0 + r_lo, p_hi = pos0 + r_hi;
-  const bool live_lo = r_lo < nrows, live_hi = r_hi < nrows;
-  const int warp_p_lo = pos0 + rw * 16, warp_p_hi = warp_p_lo + 15;
+  const int p_lo = HEADS ? pos0 : pos0 + r_lo, p_hi = HEADS ? pos0 : pos0 + r_hi;      // HEADS: one row, its heads
+  const bool live_lo = HEADS ? r_lo < a.Hq : r_lo < nrows, live_hi = HEADS ? r_hi < a.Hq : r_hi < nrows;
+  const int warp_p_lo = pos0 + rw * 16, warp_p_hi = HEADS ? pos0 : warp_p_lo + 15;
+  const int heads_per_v = a.Hq / a.Hv;
+  const int v_lo = r_lo / heads_per_v, v_hi = r_hi / heads_per_v;                      // HEADS: the rows' value heads
 
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float o[DVP / 8][4];
@@ -187,7 +201,7 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
     copy_wait<1>();                                 // tile t (and Q) have landed
     __syncthreads();
     const bf16* kb = Ks + buf * BN * LDK;
-    const bf16* vb = Vs + buf * BN * LDV;
+    const bf16* vb = Vs + buf * BN * ldv;
     const bool kept_run = t < nA;
     const int j0 = kept_run ? t * BN : kv0 + (t - nA) * BN;
     const int jend = kept_run ? endA : hi;
@@ -286,15 +300,40 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
             }
           }
         }
-#pragma unroll
-        for (int dp = 0; dp < DVP / 16; ++dp) {
-          if (dp * 16 < Dv) {
-            uint32_t vf[4];
-            ldm4_t(sm_u32(vb + ((np0 + kb16) * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDV + dp * 16 + 8 * (lane / 16)), vf);
+        if constexpr (HEADS) {
+          for (int v = 0; v < a.Hv; ++v) {          // the weights of value head v's query heads, the other rows zero
+            uint32_t pm[WIDE_TERMS][4];
 #pragma unroll
             for (int term = 0; term < WIDE_TERMS; ++term) {
-              mma_bf16(o[2 * dp], pt[term], vf[0], vf[1]);
-              mma_bf16(o[2 * dp + 1], pt[term], vf[2], vf[3]);
+              pm[term][0] = v_lo == v ? pt[term][0] : 0u;
+              pm[term][1] = v_hi == v ? pt[term][1] : 0u;
+              pm[term][2] = v_lo == v ? pt[term][2] : 0u;
+              pm[term][3] = v_hi == v ? pt[term][3] : 0u;
+            }
+#pragma unroll
+            for (int dp = 0; dp < DVP / 16; ++dp) {
+              if (dp * 16 < Dv) {
+                uint32_t vf[4];
+                ldm4_t(sm_u32(vb + ((np0 + kb16) * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * ldv + v * Dv + dp * 16 + 8 * (lane / 16)), vf);
+#pragma unroll
+                for (int term = 0; term < WIDE_TERMS; ++term) {
+                  mma_bf16(o[2 * dp], pm[term], vf[0], vf[1]);
+                  mma_bf16(o[2 * dp + 1], pm[term], vf[2], vf[3]);
+                }
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int dp = 0; dp < DVP / 16; ++dp) {
+            if (dp * 16 < Dv) {
+              uint32_t vf[4];
+              ldm4_t(sm_u32(vb + ((np0 + kb16) * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDV + dp * 16 + 8 * (lane / 16)), vf);
+#pragma unroll
+              for (int term = 0; term < WIDE_TERMS; ++term) {
+                mma_bf16(o[2 * dp], pt[term], vf[0], vf[1]);
+                mma_bf16(o[2 * dp + 1], pt[term], vf[2], vf[3]);
+              }
             }
           }
         }
@@ -329,9 +368,10 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
       my[(g + 8) * PS + DVP + 1] = l_hi;
     }
     __syncthreads();
-    const float sk = a.sinks ? a.sinks[h] * 1.4426950408889634f : 0.f;
-    for (int idx = tid; idx < nrows * Dv; idx += THREADS) {
+    const int n_out = HEADS ? a.Hq : nrows;         // HEADS: tile row r is query head r of the entry's one row
+    for (int idx = tid; idx < n_out * Dv; idx += THREADS) {
       const int r = idx / Dv, d = idx - r * Dv;
+      const int oh = HEADS ? r : h;
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < NW; ++w) M = fmaxf(M, mg[(w * 16 + r) * PS + DVP]);
@@ -343,15 +383,15 @@ __global__ void __launch_bounds__(BM * 2, 1) attention_prefill_wide_kernel(WideA
         L += f * pw[DVP + 1];
         O += f * pw[d];
       }
-      const size_t row = (size_t)(row0 + r);
+      const size_t row = (size_t)(row0 + (HEADS ? 0 : r));
       if (gridDim.z > 1) {
-        float* pp = a.parts + ((row * a.Hq + h) * gridDim.z + blockIdx.z) * (size_t)(Dv + 2);
+        float* pp = a.parts + ((row * a.Hq + oh) * gridDim.z + blockIdx.z) * (size_t)(Dv + 2);
         pp[d] = O;
         if (d == 0) { pp[Dv] = M; pp[Dv + 1] = L; }
       } else {
-        if (a.sinks) L += exp2f(sk - (M == -INFINITY ? 0.f : M * a.scale_log2));
+        if (a.sinks) L += exp2f(a.sinks[oh] * 1.4426950408889634f - (M == -INFINITY ? 0.f : M * a.scale_log2));
         const float v = L > 0.f ? O / L : 0.f;
-        const size_t at = (row * a.Hq + h) * Dv + d;
+        const size_t at = (row * a.Hq + oh) * Dv + d;
         if (a.out_f32) ((float*)a.out)[at] = v;
         else ((bf16*)a.out)[at] = __float2bfloat16(v);
       }
@@ -411,18 +451,24 @@ __global__ void wide_combine_kernel(WideArgs a, int Z) {
   }
 }
 
-template <int KDP, int DVP, int BM, int BN, bool NARROW>
+// Shared memory of a CTA: the query rows, two key tiles, two value tiles (the HEADS form: of all value heads).
+size_t wide_smem_bytes(int form, int KDP, int DVP, int BM, int BN, int Hv, int Dv) {
+  const size_t ldv = form == 2 ? (size_t)Hv * Dv + 8 : (size_t)DVP + 8;
+  return ((size_t)((form ? 16 : BM) + 2 * BN) * (KDP + 8) + (size_t)2 * BN * ldv) * sizeof(bf16);
+}
+
+template <int KDP, int DVP, int BM, int BN, int FORM>
 int launch_wide(const WideArgs& a, int max_tiles, int splits, cudaStream_t s) {
-  const size_t smem = ((size_t)((NARROW ? 16 : BM) + 2 * BN) * (KDP + 8) + (size_t)2 * BN * (DVP + 8)) * sizeof(bf16);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_wide_kernel<KDP, DVP, BM, BN, NARROW>,
+  const size_t smem = wide_smem_bytes(FORM, KDP, DVP, BM, BN, a.Hv, a.Dv);
+  static size_t allowed = 0;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_wide_kernel<KDP, DVP, BM, BN, FORM>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_done = true;
+    allowed = smem;
   }
-  const int Z = NARROW ? splits : 1;
-  attention_prefill_wide_kernel<KDP, DVP, BM, BN, NARROW><<<dim3(max_tiles, a.Hq, Z), BM * 2, smem, s>>>(a);
+  const int Z = FORM ? splits : 1;
+  attention_prefill_wide_kernel<KDP, DVP, BM, BN, FORM><<<dim3(max_tiles, FORM == 2 ? 1 : a.Hq, Z), BM * 2, smem, s>>>(a);
   if (Z > 1) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
@@ -431,12 +477,17 @@ int launch_wide(const WideArgs& a, int max_tiles, int splits, cudaStream_t s) {
   NV_RETURN_LAST();
 }
 
-template <int KDP, int BM, int BN, bool NARROW>
+template <int KDP, int BM, int BN, int FORM>
 int launch_wide_v(const WideArgs& a, int max_tiles, int splits, cudaStream_t s) {
-  if (a.Dv <= 64) return launch_wide<KDP, 64, BM, BN, NARROW>(a, max_tiles, splits, s);
-  if (a.Dv <= 128) return launch_wide<KDP, 128, BM, BN, NARROW>(a, max_tiles, splits, s);
-  return launch_wide<KDP, 256, BM, BN, NARROW>(a, max_tiles, splits, s);
+  if (a.Dv <= 64) return launch_wide<KDP, 64, BM, BN, FORM>(a, max_tiles, splits, s);
+  if (a.Dv <= 128) return launch_wide<KDP, 128, BM, BN, FORM>(a, max_tiles, splits, s);
+  return launch_wide<KDP, 256, BM, BN, FORM>(a, max_tiles, splits, s);
 }
+
+// The narrow forms' tile of keys for a key length.
+int narrow_bn(int KD) { return KD <= 256 ? 64 : 32; }
+int round_kd(int KD) { return KD <= 64 ? 64 : KD <= 128 ? 128 : KD <= 256 ? 256 : 512; }
+int round_dv(int Dv) { return Dv <= 64 ? 64 : Dv <= 128 ? 128 : 256; }
 
 }  // namespace
 
@@ -447,6 +498,14 @@ NV_API int nv_attention_prefill_wide_tile_rows() { return 64; }
 NV_API int nv_attention_prefill_wide_usable(int D, int KS, int Dv) {
   const int KD = D * KS;
   return D > 0 && KS > 0 && D % 8 == 0 && KD % 16 == 0 && KD <= 512 && Dv > 0 && Dv % 16 == 0 && Dv <= 256;
+}
+
+// Whether the HEADS form takes these sizes: every query head reads the same keys, at most 16 query heads, and two
+// tiles of all value heads' values fit beside the keys in a CTA's shared memory.
+NV_API int nv_attention_wide_heads_usable(int D, int KS, int Dv, int Hq, int Hk, int Hv) {
+  if (!nv_attention_prefill_wide_usable(D, KS, Dv) || KS != Hk || Hq < 1 || Hq > 16 || Hv < 1 || Hq % Hv) return 0;
+  const int KD = D * KS, bn = narrow_bn(KD);
+  return wide_smem_bytes(2, round_kd(KD), round_dv(Dv), bn, bn, Hv, Dv) <= (size_t)220 * 1024;
 }
 
 NV_API int nv_attention_prefill_wide(const void* q, const void* kc, const void* vc, const int* block_table,
@@ -460,6 +519,7 @@ NV_API int nv_attention_prefill_wide(const void* q, const void* kc, const void* 
   if (((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)out & 7)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0) return NV_OK;
   if (max_rows <= 0) max_rows = INT_MAX;
+  if (narrow == 2) max_rows = 1;                    // the tile's rows are the heads of one row
   if (narrow) {
     if (max_rows > 16) max_rows = 16;               // one tile of 16 rows per entry
     if (splits < 1) splits = 1;
@@ -473,14 +533,21 @@ NV_API int nv_attention_prefill_wide(const void* q, const void* kc, const void* 
   a.S = S; a.max_blocks = max_blocks; a.window = window; a.keep_first = keep_first; a.Hq = Hq; a.Hk = Hk; a.Hv = Hv;
   a.D = D; a.KS = KS; a.Dv = Dv; a.page = page; a.min_rows = min_rows; a.max_rows = max_rows; a.parts = parts;
   const int KD = D * KS;
-  if (narrow) {
-    if (KD <= 64) return launch_wide_v<64, 64, 64, true>(a, S, splits, stream);
-    if (KD <= 128) return launch_wide_v<128, 64, 64, true>(a, S, splits, stream);
-    if (KD <= 256) return launch_wide_v<256, 64, 64, true>(a, S, splits, stream);
-    return launch_wide_v<512, 32, 32, true>(a, S, splits, stream);
+  if (narrow == 2) {
+    if (!nv_attention_wide_heads_usable(D, KS, Dv, Hq, Hk, Hv)) return NV_ERR_UNSUPPORTED;
+    if (KD <= 64) return launch_wide_v<64, 64, 64, 2>(a, S, splits, stream);
+    if (KD <= 128) return launch_wide_v<128, 64, 64, 2>(a, S, splits, stream);
+    if (KD <= 256) return launch_wide_v<256, 64, 64, 2>(a, S, splits, stream);
+    return launch_wide_v<512, 32, 32, 2>(a, S, splits, stream);
   }
-  if (KD <= 64) return launch_wide_v<64, 128, 64, false>(a, max_tiles, 1, stream);
-  if (KD <= 128) return launch_wide_v<128, 128, 64, false>(a, max_tiles, 1, stream);
-  if (KD <= 256) return launch_wide_v<256, 128, 64, false>(a, max_tiles, 1, stream);
-  return launch_wide_v<512, 64, 32, false>(a, max_tiles, 1, stream);
+  if (narrow) {
+    if (KD <= 64) return launch_wide_v<64, 64, 64, 1>(a, S, splits, stream);
+    if (KD <= 128) return launch_wide_v<128, 64, 64, 1>(a, S, splits, stream);
+    if (KD <= 256) return launch_wide_v<256, 64, 64, 1>(a, S, splits, stream);
+    return launch_wide_v<512, 32, 32, 1>(a, S, splits, stream);
+  }
+  if (KD <= 64) return launch_wide_v<64, 128, 64, 0>(a, max_tiles, 1, stream);
+  if (KD <= 128) return launch_wide_v<128, 128, 64, 0>(a, max_tiles, 1, stream);
+  if (KD <= 256) return launch_wide_v<256, 128, 64, 0>(a, max_tiles, 1, stream);
+  return launch_wide_v<512, 64, 32, 0>(a, max_tiles, 1, stream);
 }

@@ -471,7 +471,7 @@ def attention_prefill_wide_tile_rows() -> int:
 def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
                            window: int, out, Hq: int, Hkv: int, D: int, Dv: int, *, keep_first: int = 0, sinks=None,
                            key_span: int = 1, min_rows: int = 1, max_rows: int = 0, narrow: bool = False,
-                           max_keys: int = 0) -> None:
+                           heads: bool = False, max_keys: int = 0) -> None:
     """bfloat16 rows of any mix of portions (single rows too) against paged keys of ``D`` and values of ``Dv``
     elements, on the tensor cores with float32 softmax weights (three bfloat16 terms).  ``q`` [T, Hq * key_span * D]:
     with ``key_span`` = Hkv > 1 a query head is scored against all kv heads' keys side by side (queries mixed across
@@ -483,7 +483,11 @@ def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0
     ``narrow``: the form for entries of at most ``attention_wide_narrow_rows()`` rows, decoded tokens above all (it
     skips longer entries): all warps of a CTA work on the entry's rows and share out the keys, and when the step has
     too few entries and heads to fill the multiprocessors, several CTAs share out the key tiles of one entry and head
-    and a second kernel merges them (``max_keys``: the most keys any such entry reads, which bounds the shares)."""
+    and a second kernel merges them (``max_keys``: the most keys any such entry reads, which bounds the shares).
+
+    ``heads`` (where ``attention_wide_heads_usable``): the form for entries of exactly one row whose query heads all
+    read the same keys: a CTA takes all heads of the row, so the keys are read once for them (it skips every other
+    entry)."""
     _cuda_contig(q, k_cache, v_cache, block_table, cu_rows, entry_pos0, out, sinks)
     _i32(block_table, cu_rows, entry_pos0)
     _f32(sinks)
@@ -497,10 +501,12 @@ def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0
     _need(sinks is None or sinks.numel() == Hq, "attention_prefill_wide: one sink per head")
     S = entry_pos0.numel()
     splits, parts = 1, None
+    narrow = narrow or heads
     if narrow:
         max_tiles = S
-        ctas = max(1, S * Hq)
-        key_tiles = max(1, (max(1, max_keys) + 63) // 64)
+        ctas = max(1, S if heads else S * Hq)
+        tile = 64 if key_span * D <= 256 else 32
+        key_tiles = max(1, (max(1, max_keys) + tile - 1) // tile)
         splits = max(1, min(32, key_tiles, (2 * num_sms() + ctas - 1) // ctas))
         if splits > 1:
             parts = torch.empty(T * Hq * splits * (Dv + 2), dtype=torch.float32, device=q.device)
@@ -508,8 +514,14 @@ def attention_prefill_wide(q, k_cache, v_cache, block_table, cu_rows, entry_pos0
                                            _p(cu_rows), _p(entry_pos0), S, max_tiles, scale, window,
                                            keep_first, _p(sinks), _p(out), (1 if out.dtype == torch.float32 else 0), Hq,
                                            Hkv, v_cache.shape[1], D, key_span, Dv, k_cache.shape[2], min_rows,
-                                           max_rows, (1 if narrow else 0), splits, _p(parts), _stream()),
+                                           max_rows, (2 if heads else 1 if narrow else 0), splits, _p(parts), _stream()),
            "attention_prefill_wide")
+
+
+def attention_wide_heads_usable(D: int, key_span: int, Dv: int, Hq: int, Hkv: int, Hv: int) -> bool:
+    """Whether the ``heads`` form of ``attention_prefill_wide`` takes these sizes (``key_span`` = Hkv, at most 16 query
+    heads, the value heads' tiles fit in shared memory)."""
+    return bool(lib().nv_attention_wide_heads_usable(D, key_span, Dv, Hq, Hkv, Hv))
 
 
 def attention_wide_narrow_rows() -> int:

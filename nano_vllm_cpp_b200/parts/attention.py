@@ -235,16 +235,20 @@ class PagedAttention(Mixer):
         turned = vp is not None and vp.rotary_dim > 0
         att = torch.empty((T, Hq * Dv), dtype=torch.float32 if turned else ctx.act_dtype, device=dev)
         if fast:
-            # A step that holds entries of one row sends its short entries (up to 16 rows) to the narrow form, where
-            # a CTA's warps share out the keys of one entry; the longer entries go to the form that gives a warp 16
-            # rows of a tile, in the same step if it holds both kinds.
-            short = ops.attention_wide_narrow_rows() if batch.n_single else 0
-            if short:
+            # A step that holds entries of one row sends them to a form of their own: where all query heads read the
+            # same keys (mixed heads, or one kv head) and are at most 16, a CTA takes all heads of a row and reads
+            # its keys once; else the narrow form, which also takes the step's other short entries (up to 16 rows)
+            # and in which a CTA's warps share out the keys of one entry and head.  The longer entries go to the form
+            # that gives a warp 16 rows of a tile, in the same step if it holds both kinds.
+            short = 0
+            if batch.n_single:
+                by_heads = ops.attention_wide_heads_usable(D, span, Dv, Hq, Hkv, cache.v.shape[1])
+                short = 1 if by_heads else ops.attention_wide_narrow_rows()
                 context = batch.max_context if batch.decode_only else max(batch.max_single_context, short)
                 keys = min(context, self.window + self.keep_first + short) if self.window > 0 else context
                 ops.attention_prefill_wide(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, batch.S, self.scale,
                                            self.window, att, Hq, Hkv, D, Dv, keep_first=self.keep_first,
-                                           sinks=self.sinks, key_span=span, narrow=True, max_keys=keys)
+                                           sinks=self.sinks, key_span=span, narrow=True, heads=by_heads, max_keys=keys)
             if batch.n_single < batch.S:
                 tiles = batch.T // ops.attention_prefill_wide_tile_rows() + batch.S
                 ops.attention_prefill_wide(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,

@@ -297,10 +297,14 @@ def test_window_attention_alone(dtype, layer, fast):
 
 @pytest.mark.parametrize("layer", [ps.attention_layer(heads=4, kv_heads=2, dim=32, vdim=48, window=300, keep_first=5, rot_dims=16, base=500.0, scale=0.2),
                                    ps.attention_layer(heads=2, kv_heads=1, dim=64, vdim=32, window=90, keep_first=70, rot_dims=32, base=1e4, scale=0.15),
-                                   ps.attention_layer(heads=3, kv_heads=3, dim=128, vdim=144, window=1000, keep_first=0, rot_dims=0, base=50.0, scale=0.1)])
+                                   ps.attention_layer(heads=3, kv_heads=3, dim=128, vdim=144, window=1000, keep_first=0, rot_dims=0, base=50.0, scale=0.1),
+                                   ps.attention_layer(heads=20, kv_heads=2, dim=16, vdim=32, window=200, keep_first=9, rot_dims=8, base=300.0, scale=0.25),
+                                   ps.attention_layer(heads=16, kv_heads=4, dim=32, vdim=16, window=150, keep_first=1, rot_dims=32, base=1e3, scale=0.2)])
 def test_short_entries_far_into_a_sequence(layer):
     """Single rows and portions of 2 to 16 rows hundreds of positions into a sequence, beside a longer portion of
-    another request: in a bfloat16 run the short entries' keys are shared out among warps and blocks and merged."""
+    another request: in a bfloat16 run the short entries' keys are shared out among warps and blocks and merged, and
+    with at most 16 query heads a single row's heads are worked on together (sizes: 2 to 20 heads, sixteen heads on
+    four value heads, three value heads of one query head each)."""
     width = 80
     W = ps.mixer_weights(layer, width, 41)
     part, cache, ctx = mixer_setup(layer, width, W, torch.bfloat16, True, pages=64)
