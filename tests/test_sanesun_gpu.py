@@ -508,7 +508,7 @@ def test_latent_attention_reads_a_far_key(T, i, j, decoded, dtype):
 # ---- the feed-forward and the layer
 @pytest.mark.parametrize("fast", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,ff,pq", [(64, 48, (0.3, -0.7)), (96, 120, (-2.0, 1.5)), (256, 384, (0.0, 0.0)),
+@pytest.mark.parametrize("width,ff,pq", [(64, 48, (0.3, -0.7)), (96, 120, (-2.0, 1.5)), (256, 320, (0.0, 0.0)),
                                          (80, 8, (3.0, 3.0))])
 def test_xielu_mlp_alone(dtype, width, ff, pq, fast):
     """Both branches of the activation with several pairs of its two numbers; one row, a handful and hundreds."""
