@@ -64,13 +64,18 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 // What a product's launcher takes in its `swiglu` argument: 0 nothing, 1 the SwiGLU pairing of gate and up rows, or a
-// unary activation of every output value (after the bias): 2 gelu in its erf form, 3 gelu in its tanh form, 4 silu.
+// unary activation of every output value (after the bias): 2 gelu in its erf form, 3 gelu in its tanh form, 4 silu,
+// 5 xIELU with the two positive numbers (p0, p1) that the launcher takes beside it: z > 0: p0 z^2 + z / 2; z <= 0:
+// p1 (e^z - 1 - z) + z / 2.
 #define NV_EPI_SWIGLU 1
 #define NV_EPI_GELU_ERF 2
 #define NV_EPI_GELU_TANH 3
 #define NV_EPI_SILU 4
-__device__ __forceinline__ float epilogue_act(int act, float v) {
+#define NV_EPI_XIELU 5
+#define NV_EPI_LAST NV_EPI_XIELU
+__device__ __forceinline__ float epilogue_act(int act, float v, float p0 = 0.f, float p1 = 0.f) {
   if (act == 0) return v;
+  if (act == NV_EPI_XIELU) return v > 0.f ? fmaf(p0 * v, v, 0.5f * v) : fmaf(p1, expm1f(v) - v, 0.5f * v);
   if (act == NV_EPI_GELU_ERF) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
   if (act == NV_EPI_GELU_TANH) return 0.5f * v * (1.f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
   return v / (1.f + expf(-v));

@@ -306,6 +306,7 @@ ADD_RMSNORM_MAX_MIX = 64
 
 
 EPILOGUE_ACTS = {"gelu_erf": 2, "gelu_tanh": 3, "silu": 4}
+EPILOGUE_XIELU = 5          # given as the tuple ("xielu", p0, p1) with its two positive numbers
 
 
 def _epilogue(swiglu: bool, act) -> int:
@@ -313,8 +314,16 @@ def _epilogue(swiglu: bool, act) -> int:
     of a unary activation that every output value passes after the bias."""
     if act is None:
         return 1 if swiglu else 0
+    if isinstance(act, tuple):
+        _need(not swiglu and len(act) == 3 and act[0] == "xielu", "a product's activation with numbers is ('xielu', p0, p1)")
+        return EPILOGUE_XIELU
     _need(not swiglu and act in EPILOGUE_ACTS, f"a product's activation is one of {sorted(EPILOGUE_ACTS)} and excludes swiglu")
     return EPILOGUE_ACTS[act]
+
+
+def _act_numbers(act):
+    """The two numbers that a product's launcher takes beside the activation's code (0, 0 where it has none)."""
+    return (float(act[1]), float(act[2])) if isinstance(act, tuple) else (0.0, 0.0)
 
 
 def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles=None, act=None) -> None:
@@ -351,7 +360,7 @@ def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles
                                _p(bias), (dt(bias) if bias is not None else 0),
                                _p(out), dt(out), out.stride(0),
                                M, N, K, _epilogue(swiglu, act),
-                               _p(te), _p(tr0), _p(tr), _p(nt), max_tiles, _stream()), "gemm_plain")
+                               _p(te), _p(tr0), _p(tr), _p(nt), max_tiles, *_act_numbers(act), _stream()), "gemm_plain")
 
 
 def rowdot(a, w, out, wide: bool = False) -> None:
@@ -1228,7 +1237,7 @@ def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None, act=
     _need(bias is None or (not swiglu and bias.numel() == N), "skinny product: bias")
     _check(lib().nv_skinny_gemm(_p(a), a.stride(0), R, _p(w), N, K,
                                 _p(bias), (dt(bias) if bias is not None else 0), _p(out), dt(out),
-                                out.stride(0), _epilogue(swiglu, act), _stream()),
+                                out.stride(0), _epilogue(swiglu, act), *_act_numbers(act), _stream()),
            f"skinny_gemm N={rows_w} K={K}", 0.0, float(w.element_size() * rows_w * K))
 
 
@@ -1275,7 +1284,7 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         out.stride(0), _epilogue(swiglu, act), n_tile, splits,
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), 0, 0,
                         _p(err.t if err is not None else _global_err().t), _early(), 0, 0,
-                        0, _p(None), 0, _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+                        0, _p(None), 0, *_act_numbers(act), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
            w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
@@ -1321,7 +1330,7 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), tl.max_tiles,
                             rows_w, _p(err.t if err is not None else _global_err().t),
                             (_early() if tiles_ready else 0), x_sub, x_mod, max_ctas,
-                            _p(counter), align.TK, _stream()),
+                            _p(counter), align.TK, 0.0, 0.0, _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
 
 

@@ -34,6 +34,7 @@ struct GemmArgs {
   int bias_dt, out_dt;
   int swiglu;
   int act;                  // unary activation of the outputs (0: none; NV_EPI_* codes)
+  float act_p0, act_p1;     // its two numbers (xIELU)
 };
 
 template <typename TA, typename TW, bool SWIGLU>
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(GemmArgs g) {
       float v = acc[i][j];
       if (SWIGLU) v = silu_mul(v, acc2[i][j]);
       if (g.bias) v += ld_dt(g.bias, g.bias_dt, n);
-      st_dt(g.out, g.out_dt, orow + n, epilogue_act(g.act, v));
+      st_dt(g.out, g.out_dt, orow + n, epilogue_act(g.act, v, g.act_p0, g.act_p1));
     }
   }
 }
@@ -151,13 +152,15 @@ NV_API int nv_gemm_plain(const void* A, int a_dt, long long lda, const int* a_ro
                          void* out, int out_dt, long long ldo,
                          int M, int N, int K, int swiglu,
                          const int* tile_expert, const int* tile_row0, const int* tile_rows,
-                         const int* num_tiles, int max_tiles, cudaStream_t stream) {
+                         const int* num_tiles, int max_tiles, float act_p0, float act_p1, cudaStream_t stream) {
   if (!dt_ok(a_dt) || !dt_ok(w_dt) || !dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
-  if (M < 0 || N <= 0 || K <= 0 || swiglu < 0 || swiglu > NV_EPI_SILU) return NV_ERR_BAD_SIZE;
+  if (M < 0 || N <= 0 || K <= 0 || swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
   const int act = swiglu >= 2 ? swiglu : 0;
   swiglu = swiglu == NV_EPI_SWIGLU;
   GemmArgs g;
   g.act = act;
+  g.act_p0 = act_p0;
+  g.act_p1 = act_p1;
   g.A = A; g.W = W; g.bias = bias; g.out = out; g.a_rows = a_rows;
   g.tile_expert = tile_expert; g.tile_row0 = tile_row0; g.tile_rows = tile_rows; g.num_tiles = num_tiles;
   g.lda = lda; g.ldo = ldo; g.w_expert_stride = w_expert_stride;

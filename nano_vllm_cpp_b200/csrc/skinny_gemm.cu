@@ -41,6 +41,7 @@ struct SkArgs {
   long long ldx, ldo;       // elements
   int R, N, K, groups_n, out_dt, bias_dt;
   int act;                // unary activation of the outputs (0: none; NV_EPI_* codes)
+  float act_p0, act_p1;   // its two numbers (xIELU)
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
       if (feat < a.N && row < a.R) {
         float out = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
         if (!SWIGLU && a.bias) out += ld_dt(a.bias, a.bias_dt, feat);
-        st_dt(a.out, a.out_dt, (size_t)row * a.ldo + feat, SWIGLU ? out : epilogue_act(a.act, out));
+        st_dt(a.out, a.out_dt, (size_t)row * a.ldo + feat, SWIGLU ? out : epilogue_act(a.act, out, a.act_p0, a.act_p1));
       }
     }
   };
@@ -213,16 +214,17 @@ NV_API int nv_skinny_gemm_usable(int rows, int K, long long ldx, const void* x, 
 
 // out[r, :] for rows r < R of x (R <= 32, or 8 with swiglu); W is [N, K], or [2N, K] with swiglu.
 NV_API int nv_skinny_gemm(const void* x, long long ldx, int R, const void* w, int N, int K, const void* bias, int bias_dt,
-                          void* out, int out_dt, long long ldo, int swiglu, cudaStream_t stream) {
+                          void* out, int out_dt, long long ldo, int swiglu, float act_p0, float act_p1,
+                          cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
-  if (swiglu < 0 || swiglu > NV_EPI_SILU) return NV_ERR_BAD_SIZE;
+  if (swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
   const int act = swiglu >= 2 ? swiglu : 0;
   swiglu = swiglu == NV_EPI_SWIGLU;
   if (!nv_skinny_gemm_usable(R, K, ldx, x, w) || N <= 0 || R > nv_skinny_gemm_max_rows(swiglu)) return NV_ERR_UNSUPPORTED;
   if (bias && swiglu) return NV_ERR_BAD_SIZE;
   SkArgs a;
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out;
-  a.ldx = ldx; a.ldo = ldo; a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt; a.act = act;
+  a.ldx = ldx; a.ldo = ldo; a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt; a.act = act; a.act_p0 = act_p0; a.act_p1 = act_p1;
   a.groups_n = (N + 15) / 16;
   static int num_sms = 0;
   if (!num_sms) {

@@ -60,6 +60,7 @@ struct TcArgs {
   int k_steps_total, k_steps_per_split, splits;
   int n_tile, swiglu, dual, stages;   // swiglu and dual both mean two weight tiles per stage
   int act;                            // unary activation of the outputs after the bias (0: none; NV_EPI_* codes)
+  float act_p0, act_p1;               // its two numbers (xIELU)
   int w_per_cta;                      // output features per CTA: 128, or 256 with dual
   int n_blocks;                       // blocks of w_per_cta features
   int acc_bufs;                       // accumulator sets in TMEM: 2 when two fit, else 1
@@ -171,8 +172,8 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
     for (int j = 0; j < W; ++j) {
       if (j < valid) {
         const float v = (a.swiglu ? silu_mul(g[j], u[j]) : g[j]) + bias;
-        st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, epilogue_act(a.act, v));
-        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, epilogue_act(a.act, u[j] + bias2));
+        st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, epilogue_act(a.act, v, a.act_p0, a.act_p1));
+        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
       }
     }
     return;
@@ -189,8 +190,8 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
   if (a.act) {
 #pragma unroll
     for (int j = 0; j < W; ++j) {
-      g[j] = epilogue_act(a.act, g[j]);
-      u[j] = epilogue_act(a.act, u[j]);
+      g[j] = epilogue_act(a.act, g[j], a.act_p0, a.act_p1);
+      u[j] = epilogue_act(a.act, u[j], a.act_p0, a.act_p1);
     }
   }
   if (a.out_dt == NV_DT_BF16) {
@@ -462,8 +463,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (n2_ok) p[n2] = u[j];
             } else {
               float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
-              st_dt(a.out, a.out_dt, row * a.ldo + n, epilogue_act(a.act, v + bias));
-              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, epilogue_act(a.act, u[j] + bias2));
+              st_dt(a.out, a.out_dt, row * a.ldo + n, epilogue_act(a.act, v + bias, a.act_p0, a.act_p1));
+              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
             }
           }
         }
@@ -481,7 +482,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 // Adds split-K partial sums in split order and finishes: bias, swiglu, cast.
 __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int splits, int M_tok, int N, int swiglu,
                                       const void* __restrict__ bias, int bias_dt, void* __restrict__ out, int out_dt,
-                                      long long ldo) {
+                                      long long ldo, float act_p0, float act_p1) {
   grid_dep_wait();
   grid_dep_launch();
   const int act = swiglu >= 2 ? swiglu : 0;          // (the argument's codes: common.cuh)
@@ -499,7 +500,7 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
   }
   float v = swiglu ? silu_mul(g, u) : g;
   if (bias) v += ld_dt(bias, bias_dt, n);
-  st_dt(out, out_dt, t * ldo + n, epilogue_act(act, v));
+  st_dt(out, out_dt, t * ldo + n, epilogue_act(act, v, act_p0, act_p1));
 }
 
 // The same for a grouped product: only the rows that the tile list covers are finished (other rows of `out` belong
@@ -652,10 +653,10 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
                       int early, int x_sub, int x_mod, int max_ctas, int* tile_counter, int m_out,
-                      cudaStream_t stream) {
+                      float act_p0, float act_p1, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
-  if (swiglu < 0 || swiglu > NV_EPI_SILU) return NV_ERR_BAD_SIZE;
+  if (swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
   const int act = swiglu >= 2 ? swiglu : 0;          // (see common.cuh: what the `swiglu` argument may say)
   swiglu = swiglu == NV_EPI_SWIGLU;
   if (act && tile_expert) return NV_ERR_UNSUPPORTED; // a unary activation: dense products only
@@ -681,7 +682,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.k_steps_total = (K + BLOCK_K - 1) / BLOCK_K;
   a.splits = splits < 1 ? 1 : splits;
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
-  a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0; a.act = act;
+  a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0; a.act = act; a.act_p0 = act_p0; a.act_p1 = act_p1;
   a.early = early ? 1 : 0;
   a.x_box = x_box;
   a.x_sub = x_sub; a.x_mod = x_mod;
@@ -778,7 +779,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
       const long long outputs = (long long)a.M_out * N;
       NV_RETURN_IF(launch_dep(tc_gemm_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream,
                               (const float*)scratch, a.splits, a.M_out, N, a.act ? a.act : a.swiglu, bias, bias_dt, out,
-                              out_dt, ldo));
+                              out_dt, ldo, act_p0, act_p1));
     }
   }
   NV_RETURN_LAST();

