@@ -41,8 +41,22 @@ CONFIGS = {
                             scale=0.25, ff=48, kind="attention_2"),
          ps.delta_layer(heads=2, kv_heads=1, dim=48, vdim=72, conv=3, ff=0, rank=5, kind="channel_delta_2")],
         width=64, vocab=130),
+    # sizes that the tensor-core kernels take: window attention whose mixed key is 128 long with eight heads (a decoded
+    # row's heads in one tile) and one with twenty heads (a tile per head), latents of 64 and 128 elements (the
+    # prompt kernels of both kinds), per-head products on the tensor cores in steps of more than 64 rows
+    "W": ps.model_config(
+        [ps.latent_layer(heads=4, dim=32, vdim=48, q_rank=48, kv_rank=64, scale=0.17, ff=256),
+         ps.delta_layer(heads=4, kv_heads=2, dim=32, vdim=48, conv=3, ff=256),
+         ps.attention_layer(heads=8, kv_heads=2, dim=64, vdim=32, window=48, keep_first=4, rot_dims=32, base=5000.0,
+                            scale=0.125, ff=256),
+         ps.delta_layer(heads=4, kv_heads=2, dim=32, vdim=48, conv=3, ff=256),
+         ps.latent_layer(heads=2, dim=64, vdim=64, q_rank=32, kv_rank=128, scale=0.125, ff=0, kind="latent_attention_2"),
+         ps.attention_layer(heads=20, kv_heads=4, dim=16, vdim=16, window=100, keep_first=0, rot_dims=16, base=100.0,
+                            scale=0.25, ff=128, kind="attention_2")],
+        width=128, vocab=344, eps=1e-6, embed_scale=8.0),
 }
-SEEDS = {"U": 3, "V": 5}
+SEEDS = {"U": 3, "V": 5, "W": 7}
+NAMES = ["U", "V", "W"]
 TOL = {"float32": 1e-4, "bfloat16": 4e-2}
 
 
@@ -573,7 +587,7 @@ def test_a_layer_reads_the_stream_once():
 
 # ------------------------------------------------------------------------------- whole models through the engine
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["U", "V"])
+@pytest.mark.parametrize("name", NAMES)
 def test_whole_prompts(name, dtype, models):
     runner = make_runner(models[name][2], dtype, 256)
     st = Steps(runner)
@@ -584,7 +598,7 @@ def test_whole_prompts(name, dtype, models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["U", "V"])
+@pytest.mark.parametrize("name", NAMES)
 def test_prompt_then_token_by_token(name, dtype, models):
     """A short prompt in one step, then ninety rows one at a time (the windows pass over decoded tokens; pages
     behind every window go back, the kept first tokens' page stays; steps of the same shape are replayed from a
@@ -604,7 +618,7 @@ def test_prompt_then_token_by_token(name, dtype, models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["U", "V"])
+@pytest.mark.parametrize("name", NAMES)
 def test_portions_of_several_sizes(name, dtype, models):
     runner = make_runner(models[name][2], dtype, 256)
     st = Steps(runner)
@@ -619,7 +633,7 @@ def test_portions_of_several_sizes(name, dtype, models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["U", "V"])
+@pytest.mark.parametrize("name", NAMES)
 def test_unequal_requests_together_with_pages_used_again(name, dtype, models):
     """Three slots and 192 tokens of pages for six requests that need more in turn: portions of some beside single
     rows of others; a finished request's pages and state slot go to the next one.  Every request's logits equal
