@@ -549,5 +549,7 @@ NV_API int nv_attention_prefill_wide(const void* q, const void* kc, const void* 
   if (KD <= 64) return launch_wide_v<64, 128, 64, 0>(a, max_tiles, 1, stream);
   if (KD <= 128) return launch_wide_v<128, 128, 64, 0>(a, max_tiles, 1, stream);
   if (KD <= 256) return launch_wide_v<256, 128, 64, 0>(a, max_tiles, 1, stream);
-  return launch_wide_v<512, 64, 32, 0>(a, max_tiles, 1, stream);
+  // eight warps on a tile of 32 keys where that fits in shared memory (217 KB with values up to 128 elements)
+  if (a.Dv > 128) return launch_wide<512, 256, 64, 32, 0>(a, max_tiles, 1, stream);
+  return launch_wide_v<512, 128, 32, 0>(a, max_tiles, 1, stream);
 }
