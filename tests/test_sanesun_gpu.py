@@ -663,6 +663,84 @@ def test_unequal_requests_together_with_pages_used_again(name, dtype, models):
         check_rows(st, models, name, r, ids[r], dtype, f"{name} request {r}")
 
 
+def drawn_config(rng):
+    """A model of four to nine layers whose kinds, order and sizes are drawn: every kind at least once, up to two sets
+    of sizes per kind, layers without a feed-forward, head counts from 1 to 24, sizes that do and do not fit the
+    tensor-core kernels."""
+    width, ff = rng.choice([128, 192, 256, 320, 384]), rng.choice([256, 320, 512, 640])
+    n = rng.randint(4, 9)
+    kinds = [rng.choice(["latent", "delta", "attn"]) for _ in range(n)]
+    for must in ("latent", "delta", "attn"):
+        if must not in kinds:
+            kinds[rng.randrange(n)] = must
+
+    def latent():
+        return dict(heads=rng.choice([2, 4, 6, 8, 12]), dim=rng.choice([32, 48, 64, 96]),
+                    vdim=rng.choice([32, 48, 64, 80, 96]), q_rank=rng.choice([48, 64, 96, 128]),
+                    kv_rank=rng.choice([48, 64, 80, 96, 128, 160]), scale=rng.choice([0.125, 0.1, 0.18]))
+
+    def delta():
+        kv = rng.choice([1, 2, 4])
+        return dict(heads=kv * rng.choice([1, 2, 3]), kv_heads=kv, dim=rng.choice([16, 32, 48, 64]),
+                    vdim=rng.choice([16, 32, 48, 64, 96]), conv=rng.choice([2, 3, 4, 5]), rank=rng.choice([None, 8, 16, 24, 32]))
+
+    def attn():
+        kv, dim = rng.choice([1, 2, 3, 4, 6, 8]), rng.choice([32, 64, 96, 128])
+        return dict(heads=kv * rng.choice([1, 2, 4]), kv_heads=kv, dim=dim, vdim=rng.choice([32, 64, 96, 128]),
+                    window=rng.choice([17, 40, 64, 100, 150, 200]), keep_first=rng.choice([0, 1, 2, 4, 8, 20]),
+                    rot_dims=rng.choice([0, 16, 32, dim]), base=rng.choice([1e4, 3e4, 5e5, 100.0]),
+                    scale=rng.choice([0.125, 0.09, 0.2]))
+
+    sizes = {"latent": [latent(), latent()], "delta": [delta(), delta()], "attn": [attn(), attn()]}
+    make = {"latent": (ps.latent_layer, "latent_attention"), "delta": (ps.delta_layer, "channel_delta"),
+            "attn": (ps.attention_layer, "attention")}
+    layers = []
+    for k in kinds:
+        i = rng.randrange(2)
+        fn, base = make[k]
+        layers.append(fn(ff=rng.choice([ff, ff, ff, 0]), kind=base if i == 0 else base + "_2", **sizes[k][i]))
+    return ps.model_config(layers, width=width, vocab=rng.choice([300, 512, 1000]), eps=rng.choice([1e-6, 1e-5]),
+                           embed_scale=rng.choice([None, 4.0, 16.0]))
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_drawn_models_in_a_mixed_schedule(seed, tmp_path):
+    """Drawn models, both dtypes: five unequal requests on three slots and 576 tokens of pages, portions of up to 150
+    tokens beside single rows of others, decoding over dozens of steps, finished requests' pages and slots used
+    again; every request's logits equal the plain implementation's of the request alone."""
+    import random
+    cfg = drawn_config(random.Random(seed))
+    W = ps.random_weights(cfg, seed)
+    one = {"F": (cfg, W, ps.write_folder(cfg, W, str(tmp_path)))}
+    L = {"a": 230, "b": 90, "c": 170, "d": 45, "e": 120}
+    g = torch.Generator().manual_seed(seed)
+    ids = {r: [int(t) for t in torch.randint(0, cfg["vocab"], (n,), generator=g)] for r, n in L.items()}
+    for dtype in ("float32", "bfloat16"):
+        st = Steps(make_runner(one["F"][2], dtype, 576, max_requests=3))
+        at = {r: 0 for r in L}
+
+        def take(r, n):
+            toks = ids[r][at[r]:at[r] + n]
+            at[r] += len(toks)
+            return (r, toks)
+
+        def done(*rs):
+            return [r for r in rs if at[r] == L[r]]
+
+        st.step([take("a", 150), take("b", 2)])
+        st.step([take("a", 1), take("b", 88), take("c", 3)], end=done("b"))
+        for _ in range(30):
+            st.step([take("a", 1), take("c", 1)])
+        st.step([take("a", 49), take("c", 2), take("d", 45)], end=done("a", "d"))
+        st.step([take("c", 135), take("e", 7)], end=done("c"))
+        for _ in range(40):
+            st.step([take("e", 1)])
+        st.step([take("e", 73)], end=done("e"))
+        for r, n in L.items():
+            assert at[r] == n
+            check_rows(st, one, "F", r, ids[r], dtype, f"seed {seed} {dtype} request {r}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_cutting_does_not_change_a_row(dtype, models):
     """The same request whole, in portions and beside another request: float32 rows agree to rounding of sums,
