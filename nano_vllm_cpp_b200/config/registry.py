@@ -59,4 +59,4 @@ def architecture_name(d: dict) -> str:
 
 def _ensure_builtin() -> None:
     # The built-in architectures register themselves on import.
-    from ..models import qwen2_moe, bizodra, kifunex, sanesun  # noqa: F401
+    from ..models import qwen2_moe, bizodra, kifunex, sanesun, gekitar  # noqa: F401

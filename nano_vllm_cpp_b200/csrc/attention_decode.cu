@@ -65,6 +65,7 @@ struct DecArgs {
   int* err;
   float scale;
   int q_dt, out_dt, q_stride, max_blocks, window, Hq, Hkv, D, page, splits, stages;
+  float softcap;          // > 0: a scaled score s becomes softcap * tanh(s / softcap) (lane-per-chunk kernel only)
   int has_sink;           // the softmax's denominator also holds exp(sink): a key with that score and no value
   float sink;             // (the lane-per-chunk kernel and the merges add it; the tensor-core form does not know it)
 };
@@ -233,6 +234,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
           sc += __shfl_xor_sync(0xffffffffu, sc, 1);
           sc += __shfl_xor_sync(0xffffffffu, sc, 2);
           sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+          if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
           if (live) {
             if (sc > m[g]) {                       // a new maximum (rare after the first keys): rescale what was summed
               const float alpha = __expf(m[g] - sc);
@@ -739,7 +741,8 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
                                const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
                                int Hkv, int D, int page, int num_pages, int splits, float* scratch, int* err,
                                int* split_count, int split_count_len, int has_sink, float sink_score,
-                               int float_weights, cudaStream_t stream) {
+                               int float_weights, float softcap, cudaStream_t stream) {
+  // softcap > 0: scaled scores are capped, s -> softcap * tanh(s / softcap); like a sink it keeps the tensor-core form out.
   // has_sink: a further key with the score sink_score and no value in every softmax; it keeps the tensor-core form
   // out.  float_weights: the weights keep all their bits in their product with the values (the lane-per-chunk
   // kernel multiplies in float32; the tensor-core form takes them as three bfloat16 terms instead of one).
@@ -760,6 +763,7 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   a.part_ml = scratch ? scratch + (size_t)R * Hq * splits * D : nullptr;
   a.err = err;
   a.has_sink = has_sink; a.sink = sink_score;
+  a.softcap = softcap > 0.f ? softcap : 0.f;
   // `split_count`: zeros (R * Hq of them are enough), kept zero from launch to launch by the kernel: the splits are
   // then added up by the block that finishes last instead of by a second kernel.  For a few rows only: with many,
   // the last blocks' sums lengthen the kernel's tail by more than the second kernel's launch costs (measured per
@@ -775,7 +779,7 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   // next page is on its way while it works on one (with one stage per warp a warp sat out the whole memory latency
   // between two pages), and three CTAs of 76 KB still share a multiprocessor.  Deeper rings lose CTAs and time.
   int tc_stages = stages / WARPS * WARPS;
-  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS && !has_sink) {
+  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS && !has_sink && !(softcap > 0.f)) {
     a.stages = tc_stages;
     // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head; with
     // float_weights the weights enter the product with the values as three bfloat16 terms
@@ -860,7 +864,7 @@ NV_API int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, 
   }
   return nv_attention_decode(qkv, q_dt, q_stride, kc, vc, cache_dt, block_table, max_blocks, row_entry, positions,
                              rows, R, scale, window, out, out_dt, Hq, Hkv, D, page, num_pages, splits,
-                             g_noalloc_ptr[dev], g_noalloc_err_ptr[dev], nullptr, 0, 0, 0.f, 0, stream);
+                             g_noalloc_ptr[dev], g_noalloc_err_ptr[dev], nullptr, 0, 0, 0.f, 0, 0.f, stream);
 }
 
 NV_API int nv_attention_decode_noalloc_status(void) {

@@ -34,6 +34,8 @@ struct PfArgs {
   float scale_log2;         // scale * log2(e)
   int S, q_stride, max_blocks, window, Hq, Hkv, D, page;
   int min_rows;             // entries with fewer rows are left to another kernel
+  float softcap, cap_in;    // softcap > 0: a score s becomes softcap * tanh(s * cap_in), cap_in = scale / softcap
+                            // (scale_log2 is then log2(e) alone)
   int has_sink;             // the softmax's denominator also holds exp(sink): a key with that score and no value
   float sink_log2;          // the sink's score times log2(e)
   int terms;                // the weights enter P V as one bfloat16 term (rounded) or three (all 24 bits of the float)
@@ -193,6 +195,12 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
           mma16816(s[2 * np + 1], qa, kf[np][2], kf[np][3]);
         }
       }
+    }
+    if (a.softcap > 0.f) {
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[nt][c] = a.softcap * tanhf(s[nt][c] * a.cap_in);
     }
     // ---- mask (only on tiles that some row of the warp sees partly), online softmax
     const bool whole = j0 + BN - 1 <= warp_p_lo && (a.window <= 0 || j0 >= warp_p_hi + 1 - a.window) &&
@@ -368,14 +376,16 @@ NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, c
                                 const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                 int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,
                                 int page, int min_rows, int has_sink, float sink_score, int terms,
-                                cudaStream_t stream) {
+                                float softcap, cudaStream_t stream) {
   if (D <= 0 || D > 256 || D % 16 || Hkv <= 0 || Hq % Hkv || (terms != 1 && terms != 3)) return NV_ERR_UNSUPPORTED;
   if (q_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0) return NV_OK;
   PfArgs a;
   a.qkv = (const bf16*)qkv; a.kc = (const bf16*)kc; a.vc = (const bf16*)vc; a.block_table = block_table;
   a.cu_rows = cu_rows; a.entry_pos0 = entry_pos0; a.out = (bf16*)out;
-  a.scale_log2 = scale * 1.4426950408889634f;
+  a.scale_log2 = (softcap > 0.f ? 1.f : scale) * 1.4426950408889634f;
+  a.softcap = softcap > 0.f ? softcap : 0.f;
+  a.cap_in = softcap > 0.f ? scale / softcap : 0.f;
   a.S = S; a.q_stride = q_stride; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.D = D;
   a.page = page;
   a.min_rows = min_rows;

@@ -72,9 +72,25 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f +
 #define NV_EPI_GELU_TANH 3
 #define NV_EPI_SILU 4
 #define NV_EPI_XIELU 5
-#define NV_EPI_LAST NV_EPI_XIELU
+// 6: a second pairing of gate and up rows, with both halves clamped by p0 and the sigmoid's slope p1:
+// g = min(g, p0), u = clamp(u, -p0, p0), out = g sigmoid(p1 g) (u + 1).  7: the square of relu.
+#define NV_EPI_GLU_CLAMPED 6
+#define NV_EPI_RELU2 7
+#define NV_EPI_LAST NV_EPI_RELU2
+// Which codes pair a gate row with an up row (two accumulators per output), and the pairings themselves.
+__host__ __device__ __forceinline__ int epi_pair(int code) { return (code == NV_EPI_SWIGLU || code == NV_EPI_GLU_CLAMPED) ? code : 0; }
+__host__ __device__ __forceinline__ int epi_unary(int code) { return (code >= 2 && !epi_pair(code)) ? code : 0; }
+__device__ __forceinline__ float pair_mul(int pair, float g, float u, float p0, float p1) {
+  if (pair == NV_EPI_GLU_CLAMPED) {
+    g = fminf(g, p0);
+    u = fminf(fmaxf(u, -p0), p0);
+    return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
+  }
+  return silu_mul(g, u);
+}
 __device__ __forceinline__ float epilogue_act(int act, float v, float p0 = 0.f, float p1 = 0.f) {
   if (act == 0) return v;
+  if (act == NV_EPI_RELU2) { v = fmaxf(v, 0.f); return v * v; }
   if (act == NV_EPI_XIELU) return v > 0.f ? fmaf(p0 * v, v, 0.5f * v) : fmaf(p1, expm1f(v) - v, 0.5f * v);
   if (act == NV_EPI_GELU_ERF) return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
   if (act == NV_EPI_GELU_TANH) return 0.5f * v * (1.f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));

@@ -305,8 +305,10 @@ def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None, branch2=
 ADD_RMSNORM_MAX_MIX = 64
 
 
-EPILOGUE_ACTS = {"gelu_erf": 2, "gelu_tanh": 3, "silu": 4}
+EPILOGUE_ACTS = {"gelu_erf": 2, "gelu_tanh": 3, "silu": 4, "relu2": 7}
 EPILOGUE_XIELU = 5          # given as the tuple ("xielu", p0, p1) with its two positive numbers
+EPILOGUE_GLU_CLAMPED = 6    # with ``swiglu``: the tuple ("glu_clamped", limit, slope) makes the pairing of gate and up rows
+                            # g = min(g, limit), u = clamp(u, -limit, limit), g sigmoid(slope g) (u + 1)
 
 
 def _epilogue(swiglu: bool, act) -> int:
@@ -315,7 +317,10 @@ def _epilogue(swiglu: bool, act) -> int:
     if act is None:
         return 1 if swiglu else 0
     if isinstance(act, tuple):
-        _need(not swiglu and len(act) == 3 and act[0] == "xielu", "a product's activation with numbers is ('xielu', p0, p1)")
+        if swiglu:
+            _need(len(act) == 3 and act[0] == "glu_clamped" and act[1] > 0, "a pairing with numbers is ('glu_clamped', limit, slope)")
+            return EPILOGUE_GLU_CLAMPED
+        _need(len(act) == 3 and act[0] == "xielu", "a product's activation with numbers is ('xielu', p0, p1)")
         return EPILOGUE_XIELU
     _need(not swiglu and act in EPILOGUE_ACTS, f"a product's activation is one of {sorted(EPILOGUE_ACTS)} and excludes swiglu")
     return EPILOGUE_ACTS[act]
@@ -387,12 +392,13 @@ def attention_decode_usable(k_cache, D: int) -> bool:
 
 def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
                      Hq: int, Hkv: int, D: int, max_context: int, rows=None, err=None, sink_score=None,
-                     float_weights: bool = False) -> None:
+                     float_weights: bool = False, softcap: float = 0.0) -> None:
     """One query row per request (``rows``: which batch rows; None = all) against its paged keys.  ``qkv``: rows
     whose first Hq * D elements are the query heads.  ``sink_score``: a further key with that score and no value
     in every softmax.  ``float_weights``: the weights keep all their bits in the product with the values (the
     tensor-core form takes them as three bfloat16 terms instead of one rounded one; the kernel that gives a lane a
-    chunk of a key, which other head sizes and a sink go to, multiplies in float32)."""
+    chunk of a key, which other head sizes and a sink go to, multiplies in float32).  ``softcap`` > 0: a scaled score s
+    becomes ``softcap * tanh(s / softcap)`` (the lane-per-chunk kernel)."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, row_entry, positions, out, rows)
     _i32(block_table, row_entry, positions, rows)
     R = qkv.shape[0] if rows is None else rows.numel()
@@ -410,7 +416,7 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
                                  splits, _p(scratch), _p(err.t if err is not None else _global_err().t),
                                  _p(counts), (counts.numel() if counts is not None else 0),
                                  (0 if sink_score is None else 1), float(sink_score or 0.0),
-                                 (1 if float_weights else 0), _stream()),
+                                 (1 if float_weights else 0), float(softcap), _stream()),
            "attention_decode")
 
 
@@ -432,7 +438,7 @@ def attention_prefill_tile_rows() -> int:
 
 def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
                       window: int, out, Hq: int, Hkv: int, D: int, err=None, min_rows: int = 1,
-                      kernel: str = "auto", sink_score=None, weight_terms: int = 1) -> None:
+                      kernel: str = "auto", sink_score=None, weight_terms: int = 1, softcap: float = 0.0) -> None:
     """bfloat16 rows of any mix of portions against their paged keys: the tcgen05 kernel for head sizes 64 and
     128 and pages of 16, 32 or 64 keys, else the mma.sync kernel (``kernel="mma"`` asks for that one).  Entries
     with fewer than ``min_rows`` rows are skipped and their rows of ``out`` left as they are.
@@ -449,7 +455,7 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     page = k_cache.shape[2]
     _need(kernel in ("auto", "mma"), "attention_prefill: kernel is 'auto' or 'mma'")
     _need(weight_terms in (1, 3), "attention_prefill: the weights are one bfloat16 term or three")
-    if sink_score is not None:
+    if sink_score is not None or softcap > 0:     # (capped scores, s -> softcap * tanh(s / softcap), are the mma.sync kernel's too)
         kernel = "mma"
     if kernel == "auto" and L.nv_attention_prefill_tc_usable(D, page):
         _check(L.nv_attention_prefill_tc(_p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache),
@@ -464,7 +470,7 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
                                   block_table.shape[1], _p(cu_rows), _p(entry_pos0), S,
                                   max_tiles, scale, window, _p(out), Hq, Hkv,
                                   D, page, min_rows, (0 if sink_score is None else 1), float(sink_score or 0.0),
-                                  weight_terms, _stream()), "attention_prefill")
+                                  weight_terms, float(softcap), _stream()), "attention_prefill")
 
 
 def attention_prefill_wide_usable(D: int, key_span: int, Dv: int) -> bool:
@@ -826,7 +832,7 @@ def sample_nucleus(logits, params, recent, recent_off, out) -> None:
 
 
 # ----------------------------------------------------------------------------- state mixers and their layer pieces
-ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "xielu": 3}
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "xielu": 3, "relu2": 4}
 
 
 def _f32(*ts) -> None:
@@ -835,10 +841,14 @@ def _f32(*ts) -> None:
             _need(t.dtype == torch.float32, f"tensor must be float32, found {t.dtype}")
 
 
-def branch_norm_add(x, branches, weight, eps: float, out=None, *, branch_weights=None, mix_scale: float = 1.0) -> None:
+def branch_norm_add(x, branches, weight, eps: float, out=None, *, branch_weights=None, mix_scale: float = 1.0,
+                    mix=None, next_weight=None, next_eps: float = 0.0, out32=None) -> None:
     """``x += rms(y) * weight`` row by row, and ``out`` (float32 or bfloat16, optional) = the new ``x``.
-    ``y`` is the one branch, or with ``branch_weights`` ``mix_scale * sum_b rms(branches[b]) * branch_weights[b]``.
-    ``rms(v) = v / sqrt(mean(v^2) + eps)``.  Without branches only ``out = x`` is written."""
+    ``y`` is the one branch, or with ``branch_weights`` ``mix_scale * sum_b rms(branches[b]) * branch_weights[b]``,
+    or with ``mix`` = (rows, index, weight, dense, gate_logit) the sum that has not been taken yet (see
+    ``add_rmsnorm``).  ``rms(v) = v / sqrt(mean(v^2) + eps)``.  Without branches only ``out = x`` is written.
+    ``next_weight``: ``out`` (and ``out32``, a float32 copy) is instead ``rms(x) * next_weight`` of the stream after
+    the sum, with ``next_eps``: the input of the sublayer that follows, from the same launch."""
     branches = list(branches or [])
     bws = list(branch_weights or [])
     _cuda_contig(x, weight, out, *branches, *bws)
@@ -854,9 +864,29 @@ def branch_norm_add(x, branches, weight, eps: float, out=None, *, branch_weights
     _need(out is None or out.shape == x.shape, "branch_norm_add: out shape")
     b4 = branches + [None] * (4 - len(branches))
     w4 = bws + [None] * (4 - len(bws))
+    rows = index = mweight = dense = gate = None
+    R, gate_ld = 0, 1
+    if mix is not None:
+        _need(not branches, "branch_norm_add: branches or a mix, not both")
+        rows, index, mweight, dense, gate = mix
+        _cuda_contig(rows, index, mweight, dense)
+        _f32(rows, mweight, dense, gate)
+        _i32(index)
+        R = index.shape[1]
+        _need(rows.shape[1] == H and index.shape == (T, R) and mweight.shape == (T, R)
+              and (dense is None or dense.shape == x.shape) and weight is not None and weight.numel() == H,
+              "branch_norm_add: mix shapes")
+        if gate is not None:
+            gate_ld = gate.stride(0) if gate.dim() >= 1 else 1
+    _cuda_contig(next_weight, out32)
+    _f32(next_weight, out32)
+    _need(next_weight is None or next_weight.numel() == H, "branch_norm_add: next_weight")
+    _need(out32 is None or (next_weight is not None and out32.shape == x.shape), "branch_norm_add: out32 comes with next_weight")
     _check(lib().nv_branch_norm_add(_p(x), _p(b4[0]), _p(b4[1]), _p(b4[2]), _p(b4[3]), _p(w4[0]), _p(w4[1]), _p(w4[2]),
                                     _p(w4[3]), len(branches), mix_scale, _p(weight), eps, _p(out),
-                                    (dt(out) if out is not None else 0), T, H, _stream()), "branch_norm_add")
+                                    (dt(out) if out is not None else 0), T, H, _p(rows), _p(index), _p(mweight), R,
+                                    _p(dense), _p(gate), gate_ld, _p(next_weight), float(next_eps), _p(out32),
+                                    _stream()), "branch_norm_add")
 
 
 def activation(src, out, kind: str, params=(0.0, 0.0)) -> None:
@@ -1010,12 +1040,16 @@ def gated_delta_scan(qkv, cols: dict, G: int, proj, pcols: dict, A_log, dt_bias,
 def qk_prepare_store(src, q0: int, k0: int, v0: int, positions, row_entry, block_table, q_weight, k_weight, eps: float,
                      inv_freq, rot_dim: int, interleaved: bool, amplitude: float, q_out, k_cache, v_cache,
                      Hq: int, Hkv: int, D: int, Dv: int, write_kv: bool, err: ErrorFlag, *, v_inv_freq=None,
-                     v_rot_dim: int = 0) -> None:
+                     v_rot_dim: int = 0, rot0: int = 0, k_norm_dim: int = 0, norm_always: bool = False,
+                     norm_after: bool = False) -> None:
     """Per row: q and k heads RMS-normed over D (weights may be None), their first ``rot_dim`` elements turned in
     pairs by the row's position, q to ``q_out`` [T, Hq * D], k and v to the row's place in their pages.
     ``Hq`` may be 0 (``q_out`` None: only keys and values are written) and ``v_cache`` None (only keys).
     ``v_rot_dim`` > 0: the first so many elements of every value head are turned too, in pairs
-    ``(i, i + v_rot_dim / 2)`` by ``position * v_inv_freq[i]``, before they are stored."""
+    ``(i, i + v_rot_dim / 2)`` by ``position * v_inv_freq[i]``, before they are stored.
+    ``rot0``: the turned elements are ``rot0 .. rot0 + rot_dim - 1`` of a head.  ``k_norm_dim`` > 0: a key head's norm is
+    taken over, and applied to, its first so many elements only.  ``norm_always``: heads are normed also where the
+    weight is None (the weight is then one).  ``norm_after``: the norm follows the turn instead of preceding it."""
     _cuda_contig(positions, row_entry, block_table, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache, v_inv_freq)
     _i32(positions, row_entry, block_table)
     _f32(q_weight, k_weight, inv_freq, v_inv_freq)
@@ -1024,8 +1058,11 @@ def qk_prepare_store(src, q0: int, k0: int, v0: int, positions, row_entry, block
     QP = q_out.shape[1] // Hq if Hq else D
     KP, VP = k_cache.shape[3], (v_cache.shape[3] if v_cache is not None else Dv)   # a head's elements, padded with zeros
     _need(src.stride(-1) == 1 and (Hq == 0 or q_out.shape == (T, Hq * QP)) and QP >= D, "qk_prepare_store: shapes")
-    _need(k_cache.shape[1:3] == (Hkv, page) and KP >= D and VP >= Dv, "qk_prepare_store: cache shapes")
-    _need(v_cache is None or (v_cache.shape[1:3] == (Hkv, page) and k_cache.dtype == v_cache.dtype),
+    if not write_kv or Hkv == 0:          # nothing is written: only the queries are prepared
+        KP, VP = max(KP, D), max(VP, Dv)
+    _need(not write_kv or Hkv == 0 or (k_cache.shape[1:3] == (Hkv, page) and KP >= D and VP >= Dv),
+          "qk_prepare_store: cache shapes")
+    _need(v_cache is None or not write_kv or (v_cache.shape[1:3] == (Hkv, page) and k_cache.dtype == v_cache.dtype),
           "qk_prepare_store: cache shapes")
     _need(rot_dim == 0 or inv_freq.numel() >= rot_dim // 2, "qk_prepare_store: inv_freq")
     _need(v_rot_dim == 0 or (v_inv_freq is not None and v_inv_freq.numel() >= v_rot_dim // 2), "qk_prepare_store: v_inv_freq")
@@ -1035,18 +1072,20 @@ def qk_prepare_store(src, q0: int, k0: int, v0: int, positions, row_entry, block
                                      (dt(q_out) if q_out is not None else 0),
                                      _p(k_cache), _p(v_cache), dt(k_cache), Hq, Hkv, D, Dv, page,
                                      (1 if write_kv else 0), _p(err.t), T, QP, KP, VP, _p(v_inv_freq), v_rot_dim,
+                                     rot0, k_norm_dim, (1 if norm_always else 0) | (2 if norm_after else 0),
                                      _stream()), "qk_prepare_store")
 
 
 def paged_attention_general(q, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
                             Hq: int, Hkv: int, D: int, Dv: int, sink_score=None, *, sinks=None, keep_first: int = 0,
-                            key_span: int = 1, value_heads: int | None = None) -> None:
+                            key_span: int = 1, value_heads: int | None = None, softcap: float = 0.0) -> None:
     """Causal softmax attention of every row over its request's paged keys; values may be wider or narrower than
     keys; ``sink_score``: a further key with that score and no value in every softmax (None: none), ``sinks``
     (float32 [Hq]): one such score per head; ``keep_first``: with a window, the sequence's first so many positions
     stay visible; ``key_span`` = Hkv: a query row holds Hkv * D elements per head and a score is the sum of its
     parts' products with all kv heads' keys (see ``mix_query_heads``); ``v_cache`` None: the values are read where
-    the keys are; ``value_heads``: kv heads of the values where that is not ``Hkv``."""
+    the keys are; ``value_heads``: kv heads of the values where that is not ``Hkv``; ``softcap`` > 0: a scaled score
+    s becomes ``softcap * tanh(s / softcap)`` before mask and softmax."""
     if v_cache is None:
         v_cache = k_cache
     Hv = Hkv if value_heads is None else value_heads
@@ -1062,7 +1101,7 @@ def paged_attention_general(q, k_cache, v_cache, block_table, row_entry, positio
                                             block_table.shape[1], _p(row_entry), _p(positions), scale, window,
                                             keep_first, (0 if sink_score is None else 1), float(sink_score or 0.0),
                                             _p(sinks), _p(out), dt(out), T, Hq, Hkv, Hv, D, Dv, key_span,
-                                            k_cache.shape[2], _stream()),
+                                            k_cache.shape[2], float(softcap), _stream()),
            "paged_attention_general")
 
 
@@ -1101,32 +1140,34 @@ def cols_rmsnorm(src, col0: int, n: int, w, eps: float, out) -> None:
            "cols_rmsnorm")
 
 
-def head_project(x, w, out, H: int, K: int, N: int, gate=None, gate_col: int = 0) -> None:
+def head_project(x, w, out, H: int, K: int, N: int, gate=None, gate_col: int = 0, gate_each: bool = False) -> None:
     """``out[t, h, :] = x[t, h, :] @ w[h]`` for ``x`` [T, H * K] and ``w`` [H, K, N]; with ``gate`` (float32
-    rows, column ``gate_col + h``) the head's output is multiplied by the sigmoid of its gate."""
+    rows, column ``gate_col + h``) the head's output is multiplied by the sigmoid of its gate; ``gate_each``: every
+    element has a gate of its own (column ``gate_col + h * N + n``)."""
     _cuda_contig(x, w, out)
     _f32(gate)
     T = x.shape[0]
     _need(x.shape == (T, H * K) and w.shape == (H, K, N) and out.shape == (T, H * N), "head_project: shapes")
-    _need(gate is None or (gate.stride(-1) == 1 and gate.shape[0] == T and gate.shape[1] >= gate_col + H),
+    _need(gate is None or (gate.stride(-1) == 1 and gate.shape[0] == T and gate.shape[1] >= gate_col + (H * N if gate_each else H)),
           "head_project: gate rows")
     _check(lib().nv_head_project(_p(x), dt(x), _p(w), dt(w), _p(gate), (gate.stride(0) if gate is not None else 0), gate_col,
-                                 _p(out), dt(out), T, H, K, N, _stream()), "head_project")
+                                 _p(out), dt(out), T, H, K, N, (1 if gate_each else 0), _stream()), "head_project")
 
 
 # ----------------------------------------------------------------------------- fast products
 _num_sms = None
 
 
-def head_gate(x, gate, gate_col: int, out, H: int, N: int) -> None:
+def head_gate(x, gate, gate_col: int, out, H: int, N: int, gate_each: bool = False) -> None:
     """``out[t, h, :] = x[t, h, :] * sigmoid(gate[t, gate_col + h])`` for float32 ``x`` [T, H * N] and float32 ``gate``
-    rows; ``out`` in either dtype."""
+    rows; ``out`` in either dtype; ``gate_each``: element n of head h has the gate ``gate_col + h * N + n``."""
     _cuda_contig(x, out)
     _f32(x, gate)
     T = x.shape[0]
     _need(x.shape == (T, H * N) and out.shape == x.shape and gate.stride(-1) == 1 and gate.shape[0] == T
-          and gate.shape[1] >= gate_col + H, "head_gate: shapes")
-    _check(lib().nv_head_gate(_p(x), _p(gate), gate.stride(0), gate_col, _p(out), dt(out), T, H, N, _stream()),
+          and gate.shape[1] >= gate_col + (H * N if gate_each else H), "head_gate: shapes")
+    _check(lib().nv_head_gate(_p(x), _p(gate), gate.stride(0), gate_col, _p(out), dt(out), T, H, N,
+                              (1 if gate_each else 0), _stream()),
            "head_gate")
 
 
@@ -1289,7 +1330,7 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
 
 
 def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False,
-                      x_rows=None, max_ctas: int = 0, counter=None) -> None:
+                      x_rows=None, max_ctas: int = 0, counter=None, act=None) -> None:
     """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile.
 
     ``x_rows`` = (sub, mod): a tile whose outputs are rows r.. takes rows ``(r - sub) % mod``.. of ``a`` (several
@@ -1326,11 +1367,11 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
             scratch = torch.empty((splits, align.TK, 2 * N if swiglu else N), dtype=torch.float32, device=a.device)
     _check(lib().nv_tc_gemm(_p(a), a.stride(0), a.shape[0], _p(w), E * rows_w, N,
                             K, _p(None), 0, _p(out), dt(out), out.stride(0),
-                            (1 if swiglu else 0), tl.tile_m, splits, _p(scratch), _p(tl.tile_expert),
+                            _epilogue(swiglu, act), tl.tile_m, splits, _p(scratch), _p(tl.tile_expert),
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), tl.max_tiles,
                             rows_w, _p(err.t if err is not None else _global_err().t),
                             (_early() if tiles_ready else 0), x_sub, x_mod, max_ctas,
-                            _p(counter), align.TK, 0.0, 0.0, _stream()),
+                            _p(counter), align.TK, *_act_numbers(act), _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
 
 

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(GemmArgs g) {
       int n = col0 + tx * TN + j;
       if (n >= g.N) continue;
       float v = acc[i][j];
-      if (SWIGLU) v = silu_mul(v, acc2[i][j]);
+      if (SWIGLU) v = pair_mul(g.swiglu, v, acc2[i][j], g.act_p0, g.act_p1);
       if (g.bias) v += ld_dt(g.bias, g.bias_dt, n);
       st_dt(g.out, g.out_dt, orow + n, epilogue_act(g.act, v, g.act_p0, g.act_p1));
     }
@@ -155,8 +155,8 @@ NV_API int nv_gemm_plain(const void* A, int a_dt, long long lda, const int* a_ro
                          const int* num_tiles, int max_tiles, float act_p0, float act_p1, cudaStream_t stream) {
   if (!dt_ok(a_dt) || !dt_ok(w_dt) || !dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (M < 0 || N <= 0 || K <= 0 || swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
-  const int act = swiglu >= 2 ? swiglu : 0;
-  swiglu = swiglu == NV_EPI_SWIGLU;
+  const int act = epi_unary(swiglu);
+  swiglu = epi_pair(swiglu);
   GemmArgs g;
   g.act = act;
   g.act_p0 = act_p0;

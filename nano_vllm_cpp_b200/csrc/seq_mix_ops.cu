@@ -51,9 +51,22 @@ struct BranchArgs {
   const float* br[MAX_BRANCHES];    // [T, H] branch outputs
   const float* bw[MAX_BRANCHES];    // [H] weights of the branches' own norms (all given, or none with nb == 1)
   const float* w;                   // [H] weight of the norm over the (mixed) branch
-  void* out;                        // [T, H] x after the sum, in out_dt (may be null)
+  void* out;                        // [T, H] x after the sum, in out_dt (may be null); with next_w its normed rows
   int nb, H, out_dt;
   float eps, mix_scale;
+  // The branch as a sum that has not been taken (nb == 0, R > 0 or dense given):
+  // y[t] = sigmoid(gate_logit[t]) * dense[t] + sum_r weight[t, r] * rows[index[t, r]]
+  const float* rows;
+  const int* index;
+  const float* weight;
+  int R;
+  const float* dense;
+  const float* gate_logit;
+  long long gate_ld;
+  // A second norm over the stream after the sum: out = rms(x) * next_w (and out32, a float32 copy of it)
+  const float* next_w;
+  float next_eps;
+  float* out32;
 };
 
 __global__ void __launch_bounds__(SM_THREADS) branch_norm_add_kernel(BranchArgs a) {
@@ -61,30 +74,56 @@ __global__ void __launch_bounds__(SM_THREADS) branch_norm_add_kernel(BranchArgs 
   __shared__ float red[SM_THREADS / 32];
   const int t = blockIdx.x, tid = threadIdx.x, H = a.H;
   const size_t base = (size_t)t * H;
-  if (a.nb == 0) {
-    if (a.out)
-      for (int i = tid; i < H; i += SM_THREADS) st_dt(a.out, a.out_dt, base + i, a.x[base + i]);
-    return;
-  }
-  if (a.bw[0]) {
-    for (int i = tid; i < H; i += SM_THREADS) ysm[i] = 0.f;
-    for (int b = 0; b < a.nb; ++b) {
-      float ss = 0.f;
-      for (int i = tid; i < H; i += SM_THREADS) { float v = a.br[b][base + i]; ss = fmaf(v, v, ss); }
-      const float r = rsqrtf(block_sum(ss, red) / (float)H + a.eps);
-      for (int i = tid; i < H; i += SM_THREADS) ysm[i] += a.br[b][base + i] * r * a.bw[b][i];
+  const bool mixed = a.R > 0 || a.dense != nullptr;
+  if (a.nb == 0 && !mixed) {
+    if (a.next_w) {
+      for (int i = tid; i < H; i += SM_THREADS) ysm[i] = a.x[base + i];
+    } else {
+      if (a.out)
+        for (int i = tid; i < H; i += SM_THREADS) st_dt(a.out, a.out_dt, base + i, a.x[base + i]);
+      return;
     }
-    for (int i = tid; i < H; i += SM_THREADS) ysm[i] *= a.mix_scale;
   } else {
-    for (int i = tid; i < H; i += SM_THREADS) ysm[i] = a.br[0][base + i];
+    if (mixed) {
+      const float gate = a.dense && a.gate_logit ? sigmoidf_(a.gate_logit[(size_t)t * a.gate_ld]) : 1.f;
+      for (int i = tid; i < H; i += SM_THREADS) {
+        float y = 0.f;
+        for (int k = 0; k < a.R; ++k)        // the sum keeps the order of k
+          y = fmaf(a.weight[(size_t)t * a.R + k], a.rows[(size_t)a.index[(size_t)t * a.R + k] * H + i], y);
+        if (a.dense) y = a.dense[base + i] * gate + y;
+        ysm[i] = y;
+      }
+    } else if (a.bw[0]) {
+      for (int i = tid; i < H; i += SM_THREADS) ysm[i] = 0.f;
+      for (int b = 0; b < a.nb; ++b) {
+        float ss = 0.f;
+        for (int i = tid; i < H; i += SM_THREADS) { float v = a.br[b][base + i]; ss = fmaf(v, v, ss); }
+        const float r = rsqrtf(block_sum(ss, red) / (float)H + a.eps);
+        for (int i = tid; i < H; i += SM_THREADS) ysm[i] += a.br[b][base + i] * r * a.bw[b][i];
+      }
+      for (int i = tid; i < H; i += SM_THREADS) ysm[i] *= a.mix_scale;
+    } else {
+      for (int i = tid; i < H; i += SM_THREADS) ysm[i] = a.br[0][base + i];
+    }
+    float ss = 0.f;
+    for (int i = tid; i < H; i += SM_THREADS) ss = fmaf(ysm[i], ysm[i], ss);
+    const float r = rsqrtf(block_sum(ss, red) / (float)H + a.eps);
+    for (int i = tid; i < H; i += SM_THREADS) {
+      const float v = a.x[base + i] + ysm[i] * r * a.w[i];
+      a.x[base + i] = v;
+      if (a.next_w) ysm[i] = v;
+      else if (a.out) st_dt(a.out, a.out_dt, base + i, v);
+    }
+    if (!a.next_w) return;
   }
+  // the next sublayer's input: the norm of the stream as it is now (a thread reads back what it wrote itself)
   float ss = 0.f;
   for (int i = tid; i < H; i += SM_THREADS) ss = fmaf(ysm[i], ysm[i], ss);
-  const float r = rsqrtf(block_sum(ss, red) / (float)H + a.eps);
+  const float r = rsqrtf(block_sum(ss, red) / (float)H + a.next_eps);
   for (int i = tid; i < H; i += SM_THREADS) {
-    const float v = a.x[base + i] + ysm[i] * r * a.w[i];
-    a.x[base + i] = v;
+    const float v = ysm[i] * r * a.next_w[i];
     if (a.out) st_dt(a.out, a.out_dt, base + i, v);
+    if (a.out32) a.out32[base + i] = v;
   }
 }
 
@@ -92,6 +131,7 @@ __global__ void __launch_bounds__(SM_THREADS) branch_norm_add_kernel(BranchArgs 
 // kind 3, xIELU with the two positive numbers (p0, p1): z > 0: p0 z^2 + z / 2; z <= 0: p1 (e^z - 1 - z) + z / 2
 __device__ __forceinline__ float act_of(int kind, float z, float p0 = 0.f, float p1 = 0.f) {
   if (kind == 3) return z > 0.f ? fmaf(p0 * z, z, 0.5f * z) : fmaf(p1, expm1f(z) - z, 0.5f * z);
+  if (kind == 4) { z = fmaxf(z, 0.f); return z * z; }          // the square of relu
   return kind == 0 ? gelu_erf_(z) : (kind == 1 ? gelu_tanh_(z) : siluf_(z));
 }
 
@@ -448,6 +488,10 @@ struct QkArgs {
   int Hq, Hkv, D, Dv, page, write_kv;
   int* err;
   int QP, KP, VP;           // elements per head in q_out, in the key pages and in the value pages (>= D, D, Dv; the rest is zero)
+  int rot0;                 // the turned elements are rot0 .. rot0 + rot_dim - 1 of a head
+  int k_norm_dim;           // key heads: the norm is taken over (and applied to) the first so many elements; 0: all D
+  int norm_mode;            // bit 0: q and k heads are normed also without a weight (the weight is then one);
+                            // bit 1: after the turn instead of before it
   const float* v_inv_freq;  // values are turned too: the first v_rot_dim elements of every value head, in pairs
   int v_rot_dim;            // (i, i + v_rot_dim / 2), by position * v_inv_freq[i]; 0: values are stored as projected
 };
@@ -474,20 +518,23 @@ __global__ void __launch_bounds__(QK_THREADS) qk_prepare_store_kernel(QkArgs a) 
     const bool is_q = h < a.Hq;
     const size_t src = (size_t)t * a.ld + (is_q ? a.q0 + h * D : a.k0 + (h - a.Hq) * D);
     const float* w = is_q ? a.qw : a.kw;
+    const int nd = (!is_q && a.k_norm_dim > 0) ? a.k_norm_dim : D;     // what the norm covers
+    const bool normed = w != nullptr || (a.norm_mode & 1);
+    const bool after = (a.norm_mode & 2) != 0;
     float ss = 0.f;
     for (int i = lane; i < D; i += 32) {
       const float x = ld_dt(a.in, a.in_dt, src + i);
       buf[i] = x;
-      ss = fmaf(x, x, ss);
+      if (i < nd) ss = fmaf(x, x, ss);
     }
-    if (w) {
+    if (normed && !after) {
       ss = warp_sum(ss);
-      const float r = rsqrtf(ss / (float)D + a.eps);
-      for (int i = lane; i < D; i += 32) buf[i] = buf[i] * r * w[i];
+      const float r = rsqrtf(ss / (float)nd + a.eps);
+      for (int i = lane; i < nd; i += 32) buf[i] = buf[i] * r * (w ? w[i] : 1.f);
     }
     __syncwarp();
     for (int i = lane; i < half; i += 32) {
-      const int i0 = a.interleaved ? 2 * i : i, i1 = a.interleaved ? 2 * i + 1 : i + half;
+      const int i0 = a.rot0 + (a.interleaved ? 2 * i : i), i1 = a.rot0 + (a.interleaved ? 2 * i + 1 : i + half);
       const float ang = (float)pos * a.inv_freq[i];
       const float cs = cosf(ang) * a.amplitude, sn = sinf(ang) * a.amplitude;
       const float x0 = buf[i0], x1 = buf[i1];
@@ -495,6 +542,14 @@ __global__ void __launch_bounds__(QK_THREADS) qk_prepare_store_kernel(QkArgs a) 
       buf[i1] = x1 * cs + x0 * sn;
     }
     __syncwarp();
+    if (normed && after) {
+      ss = 0.f;
+      for (int i = lane; i < nd; i += 32) ss = fmaf(buf[i], buf[i], ss);
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)nd + a.eps);
+      for (int i = lane; i < nd; i += 32) buf[i] = buf[i] * r * (w ? w[i] : 1.f);
+      __syncwarp();
+    }
     if (is_q) {
       const size_t dst = ((size_t)t * a.Hq + h) * a.QP;
       for (int i = lane; i < a.QP; i += 32) st_dt(a.q_out, a.q_dt, dst + i, i < D ? buf[i] : 0.f);
@@ -539,7 +594,7 @@ __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_entry,
     const int* __restrict__ positions, float scale, int window, int keep_first, int has_sink, float sink_score,
     const float* __restrict__ sinks, void* __restrict__ out, int out_dt, int Hq, int Hkv, int Hv, int D, int Dv,
-    int KS, int page) {
+    int KS, int page, float softcap) {
   extern __shared__ float qs[];      // KS * D
   __shared__ float p[ATTG_THREADS];
   __shared__ int pslot[ATTG_THREADS];
@@ -576,6 +631,7 @@ __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
       }
       (void)slot;
       s = acc * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     // maximum over the chunk
     float mx = warp_max(s);
@@ -676,7 +732,8 @@ __global__ void __launch_bounds__(SM_THREADS) cols_rmsnorm_kernel(const float* _
 
 // ------------------------------------------------------------------ a small product per head
 // x [T, H, K] (float32 or bfloat16), w [H, K, N] (float32 or bfloat16) -> out [T, H, N] = x[t, h, :] w[h]; with `gate` the head's
-// output is multiplied by sigmoid(gate[t, gate0 + h]).  A block takes HP_ROWS rows of one head, so a weight is read
+// output is multiplied by sigmoid(gate[t, gate0 + h]), or with `gate_each` element n of it by
+// sigmoid(gate[t, gate0 + h N + n]).  A block takes HP_ROWS rows of one head, so a weight is read
 // once for all of them; a thread owns output columns and sums over k in ascending order.
 constexpr int HP_ROWS = 8;
 constexpr int HP_THREADS = 128;
@@ -684,7 +741,7 @@ constexpr int HP_THREADS = 128;
 __global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const void* __restrict__ x, int x_dt,
                                                                   const void* __restrict__ w, int w_dt, const float* __restrict__ gate,
                                                                   long long gate_ld, int gate0, void* __restrict__ out,
-                                                                  int out_dt, int T, int H, int K, int N) {
+                                                                  int out_dt, int T, int H, int K, int N, int gate_each) {
   extern __shared__ float xs[];      // HP_ROWS * K
   const int t0 = blockIdx.x * HP_ROWS, h = blockIdx.y;
   const int rows = min(HP_ROWS, T - t0);
@@ -696,8 +753,13 @@ __global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const void* __
   float g[HP_ROWS];
 #pragma unroll
   for (int r = 0; r < HP_ROWS; ++r)
-    g[r] = gate && r < rows ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + h]) : 1.f;
+    g[r] = gate && !gate_each && r < rows ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + h]) : 1.f;
   for (int n = threadIdx.x; n < N; n += HP_THREADS) {
+    if (gate && gate_each) {
+#pragma unroll
+      for (int r = 0; r < HP_ROWS; ++r)
+        g[r] = r < rows ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + (size_t)h * N + n]) : 1.f;
+    }
     float acc[HP_ROWS];
 #pragma unroll
     for (int r = 0; r < HP_ROWS; ++r) acc[r] = 0.f;
@@ -714,13 +776,14 @@ __global__ void __launch_bounds__(HP_THREADS) head_project_kernel(const void* __
 
 // out[t, h, :] = x[t, h, :] * sigmoid(gate[t, gate0 + h]): the gate alone, for head outputs that another product made.
 __global__ void head_gate_kernel(const float* __restrict__ x, const float* __restrict__ gate, long long gate_ld, int gate0,
-                                 void* __restrict__ out, int out_dt, long long total, int H, int N) {
+                                 void* __restrict__ out, int out_dt, long long total, int H, int N, int gate_each) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long th = i / N;
   const long long t = th / H;
   const int h = (int)(th - t * H);
-  st_dt(out, out_dt, (size_t)i, x[i] * sigmoidf_(gate[t * gate_ld + gate0 + h]));
+  const long long col = gate_each ? (long long)h * N + (i - th * N) : h;     // a gate per element, or one per head
+  st_dt(out, out_dt, (size_t)i, x[i] * sigmoidf_(gate[t * gate_ld + gate0 + col]));
 }
 
 // The same for few rows (a decode step): a block takes HP_ROWS rows, one head and 32 output columns, its four warps
@@ -732,7 +795,7 @@ __global__ void __launch_bounds__(HP_THREADS) head_project_few_kernel(const void
                                                                       const void* __restrict__ w, int w_dt,
                                                                       const float* __restrict__ gate, long long gate_ld,
                                                                       int gate0, void* __restrict__ out, int out_dt, int T,
-                                                                      int H, int K, int N) {
+                                                                      int H, int K, int N, int gate_each) {
   extern __shared__ float xs[];      // HP_ROWS * K, then [4][HP_ROWS][HP_FEW_COLS] partial sums
   float* part = xs + (size_t)HP_ROWS * K;
   const int t0 = blockIdx.x * HP_ROWS, h = blockIdx.y;
@@ -765,7 +828,7 @@ __global__ void __launch_bounds__(HP_THREADS) head_project_few_kernel(const void
       float sum = 0.f;
 #pragma unroll
       for (int q = 0; q < 4; ++q) sum += part[(q * HP_ROWS + r) * HP_FEW_COLS + c];
-      const float g = gate ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + h]) : 1.f;
+      const float g = gate ? sigmoidf_(gate[(size_t)(t0 + r) * gate_ld + gate0 + (gate_each ? (size_t)h * N + nn : (size_t)h)]) : 1.f;
       st_dt(out, out_dt, ((size_t)(t0 + r) * H + h) * N + nn, sum * g);
     }
   }
@@ -1153,8 +1216,12 @@ int allow_smem(K kernel, size_t bytes) {
 NV_API int nv_branch_norm_add(float* x, const float* b0, const float* b1, const float* b2, const float* b3,
                               const float* w0, const float* w1, const float* w2, const float* w3, int nb,
                               float mix_scale, const float* w, float eps, void* out, int out_dt, int T, int H,
-                              cudaStream_t s) {
-  if (nb < 0 || nb > MAX_BRANCHES || H <= 0) return NV_ERR_BAD_SIZE;
+                              const float* rows, const int* index, const float* weight, int R, const float* dense,
+                              const float* gate_logit, long long gate_ld, const float* next_w, float next_eps,
+                              float* out32, cudaStream_t s) {
+  if (nb < 0 || nb > MAX_BRANCHES || H <= 0 || R < 0) return NV_ERR_BAD_SIZE;
+  if ((R > 0 || dense) && nb > 0) return NV_ERR_BAD_SIZE;
+  if (R > 0 && (!rows || !index || !weight)) return NV_ERR_BAD_SIZE;
   if (out && !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0) return NV_OK;
   BranchArgs a;
@@ -1167,7 +1234,9 @@ NV_API int nv_branch_norm_add(float* x, const float* b0, const float* b1, const 
     if ((bw[i] != nullptr) != (bw[0] != nullptr)) return NV_ERR_BAD_SIZE;
   }
   if (nb > 1 && !bw[0]) return NV_ERR_BAD_SIZE;
-  if (nb > 0 && !w) return NV_ERR_BAD_SIZE;
+  if ((nb > 0 || R > 0 || dense) && !w) return NV_ERR_BAD_SIZE;
+  a.rows = rows; a.index = index; a.weight = weight; a.R = R; a.dense = dense; a.gate_logit = gate_logit;
+  a.gate_ld = gate_ld; a.next_w = next_w; a.next_eps = next_eps; a.out32 = out32;
   a.w = w; a.out = out; a.nb = nb; a.H = H; a.out_dt = out_dt; a.eps = eps; a.mix_scale = mix_scale;
   const size_t smem = sizeof(float) * (size_t)H;
   int rc = allow_smem(branch_norm_add_kernel, smem);
@@ -1179,7 +1248,7 @@ NV_API int nv_branch_norm_add(float* x, const float* b0, const float* b1, const 
 NV_API int nv_activation(const void* in, int in_dt, void* out, int out_dt, long long n, int kind, float p0, float p1,
                          cudaStream_t s) {
   if (!dt_ok(in_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
-  if (kind < 0 || kind > 3) return NV_ERR_UNSUPPORTED;
+  if (kind < 0 || kind > 4) return NV_ERR_UNSUPPORTED;
   if (n == 0) return NV_OK;
   if (in_dt == NV_DT_F32 && out_dt == NV_DT_BF16 && n % 4 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 7) == 0) {
     const long long n4 = n / 4;
@@ -1283,15 +1352,17 @@ NV_API int nv_qk_prepare_store(const void* in, int in_dt, long long ld, int q0, 
                                const float* kw, float eps, const float* inv_freq, int rot_dim, int interleaved,
                                float amplitude, void* q_out, int q_dt, void* kc, void* vc, int cache_dt, int Hq,
                                int Hkv, int D, int Dv, int page, int write_kv, int* err, int T, int QP, int KP,
-                               int VP, const float* v_inv_freq, int v_rot_dim, cudaStream_t s) {
+                               int VP, const float* v_inv_freq, int v_rot_dim, int rot0, int k_norm_dim,
+                               int norm_mode, cudaStream_t s) {
   if (!dt_ok(in_dt) || !dt_ok(q_dt) || !dt_ok(cache_dt)) return NV_ERR_BAD_DTYPE;
-  if (rot_dim < 0 || rot_dim > D || rot_dim % 2 || D <= 0 || Dv <= 0) return NV_ERR_BAD_SIZE;
+  if (rot_dim < 0 || rot0 < 0 || rot0 + rot_dim > D || rot_dim % 2 || D <= 0 || Dv <= 0) return NV_ERR_BAD_SIZE;
+  if (k_norm_dim < 0 || k_norm_dim > D || norm_mode < 0 || norm_mode > 3) return NV_ERR_BAD_SIZE;
   if (v_rot_dim < 0 || v_rot_dim > Dv || v_rot_dim % 2 || (v_rot_dim && !v_inv_freq)) return NV_ERR_BAD_SIZE;
   if (QP < D || KP < D || VP < Dv) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   QkArgs a = {in, in_dt, ld, q0, k0, v0, positions, row_entry, block_table, max_blocks, qw, kw, eps, inv_freq, rot_dim,
               interleaved, amplitude, q_out, q_dt, kc, vc, cache_dt, Hq, Hkv, D, Dv, page, write_kv, err, QP, KP, VP,
-              v_inv_freq, v_rot_dim};
+              rot0, k_norm_dim, norm_mode, v_inv_freq, v_rot_dim};
   const size_t smem = sizeof(float) * (size_t)(QK_THREADS / 32) * D;
   int rc = allow_smem(qk_prepare_store_kernel, smem);
   if (rc) return rc;
@@ -1303,7 +1374,8 @@ NV_API int nv_paged_attention_general(const void* q, int q_dt, const void* kc, c
                                       const int* block_table, int max_blocks, const int* row_entry,
                                       const int* positions, float scale, int window, int keep_first, int has_sink,
                                       float sink_score, const float* sinks, void* out, int out_dt, int T, int Hq,
-                                      int Hkv, int Hv, int D, int Dv, int key_span, int page, cudaStream_t s) {
+                                      int Hkv, int Hv, int D, int Dv, int key_span, int page, float softcap,
+                                      cudaStream_t s) {
   if (!dt_ok(q_dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (D <= 0 || Dv <= 0 || Dv > ATTG_NV * ATTG_THREADS || Hkv <= 0 || Hv <= 0 || Hq % Hv || keep_first < 0)
     return NV_ERR_UNSUPPORTED;
@@ -1314,7 +1386,7 @@ NV_API int nv_paged_attention_general(const void* q, int q_dt, const void* kc, c
   if (rc) return rc;
   paged_attention_general_kernel<<<dim3(T, Hq), ATTG_THREADS, smem, s>>>(
       q, q_dt, kc, vc, cache_dt, block_table, max_blocks, row_entry, positions, scale, window, keep_first, has_sink,
-      sink_score, sinks, out, out_dt, Hq, Hkv, Hv, D, Dv, key_span, page);
+      sink_score, sinks, out, out_dt, Hq, Hkv, Hv, D, Dv, key_span, page, softcap);
   NV_RETURN_LAST();
 }
 
@@ -1351,7 +1423,7 @@ NV_API int nv_cols_rmsnorm(const float* in, long long ld, int col0, int n, const
 }
 
 NV_API int nv_head_project(const void* x, int x_dt, const void* w, int w_dt, const float* gate, long long gate_ld, int gate0,
-                           void* out, int out_dt, int T, int H, int K, int N, cudaStream_t s) {
+                           void* out, int out_dt, int T, int H, int K, int N, int gate_each, cudaStream_t s) {
   if (!dt_ok(x_dt) || !dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (H <= 0 || K <= 0 || N <= 0) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
@@ -1360,24 +1432,24 @@ NV_API int nv_head_project(const void* x, int x_dt, const void* w, int w_dt, con
     int rc = allow_smem(head_project_few_kernel, few);
     if (rc) return rc;
     head_project_few_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H, (N + HP_FEW_COLS - 1) / HP_FEW_COLS), HP_THREADS, few, s>>>(
-        x, x_dt, w, w_dt, gate, gate_ld, gate0, out, out_dt, T, H, K, N);
+        x, x_dt, w, w_dt, gate, gate_ld, gate0, out, out_dt, T, H, K, N, gate_each);
     NV_RETURN_LAST();
   }
   const size_t smem = sizeof(float) * (size_t)HP_ROWS * K;
   int rc = allow_smem(head_project_kernel, smem);
   if (rc) return rc;
   head_project_kernel<<<dim3((T + HP_ROWS - 1) / HP_ROWS, H), HP_THREADS, smem, s>>>(x, x_dt, w, w_dt, gate, gate_ld, gate0,
-                                                                                     out, out_dt, T, H, K, N);
+                                                                                     out, out_dt, T, H, K, N, gate_each);
   NV_RETURN_LAST();
 }
 
 NV_API int nv_head_gate(const float* x, const float* gate, long long gate_ld, int gate0, void* out, int out_dt, int T,
-                        int H, int N, cudaStream_t s) {
+                        int H, int N, int gate_each, cudaStream_t s) {
   if (!dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (H <= 0 || N <= 0) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   const long long total = (long long)T * H * N;
-  head_gate_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, gate, gate_ld, gate0, out, out_dt, total, H, N);
+  head_gate_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, gate, gate_ld, gate0, out, out_dt, total, H, N, gate_each);
   NV_RETURN_LAST();
 }
 

@@ -41,6 +41,7 @@ struct SkArgs {
   long long ldx, ldo;       // elements
   int R, N, K, groups_n, out_dt, bias_dt;
   int act;                // unary activation of the outputs (0: none; NV_EPI_* codes)
+  int pair;               // which pairing of gate and up rows (NV_EPI_SWIGLU or NV_EPI_GLU_CLAMPED) when there is one
   float act_p0, act_p1;   // its two numbers (xIELU)
 };
 
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
       }
       const int feat = n0 + l / 4 + 8 * (j / 2), row = 8 * t + 2 * (l % 4) + (j % 2);
       if (feat < a.N && row < a.R) {
-        float out = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
+        float out = SWIGLU ? pair_mul(a.pair, v[0], v[NA - 1], a.act_p0, a.act_p1) : v[0];
         if (!SWIGLU && a.bias) out += ld_dt(a.bias, a.bias_dt, feat);
         st_dt(a.out, a.out_dt, (size_t)row * a.ldo + feat, SWIGLU ? out : epilogue_act(a.act, out, a.act_p0, a.act_p1));
       }
@@ -218,13 +219,13 @@ NV_API int nv_skinny_gemm(const void* x, long long ldx, int R, const void* w, in
                           cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
-  const int act = swiglu >= 2 ? swiglu : 0;
-  swiglu = swiglu == NV_EPI_SWIGLU;
+  const int act = epi_unary(swiglu);
+  swiglu = epi_pair(swiglu);
   if (!nv_skinny_gemm_usable(R, K, ldx, x, w) || N <= 0 || R > nv_skinny_gemm_max_rows(swiglu)) return NV_ERR_UNSUPPORTED;
   if (bias && swiglu) return NV_ERR_BAD_SIZE;
   SkArgs a;
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out;
-  a.ldx = ldx; a.ldo = ldo; a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt; a.act = act; a.act_p0 = act_p0; a.act_p1 = act_p1;
+  a.ldx = ldx; a.ldo = ldo; a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt; a.act = act; a.pair = swiglu; a.act_p0 = act_p0; a.act_p1 = act_p1;
   a.groups_n = (N + 15) / 16;
   static int num_sms = 0;
   if (!num_sms) {

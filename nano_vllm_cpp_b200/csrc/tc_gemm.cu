@@ -171,7 +171,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
 #pragma unroll
     for (int j = 0; j < W; ++j) {
       if (j < valid) {
-        const float v = (a.swiglu ? silu_mul(g[j], u[j]) : g[j]) + bias;
+        const float v = (a.swiglu ? pair_mul(a.swiglu, g[j], u[j], a.act_p0, a.act_p1) : g[j]) + bias;
         st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, epilogue_act(a.act, v, a.act_p0, a.act_p1));
         if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
       }
@@ -180,7 +180,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
   }
   if (a.swiglu) {
 #pragma unroll
-    for (int j = 0; j < W; ++j) g[j] = silu_mul(g[j], u[j]);
+    for (int j = 0; j < W; ++j) g[j] = pair_mul(a.swiglu, g[j], u[j], a.act_p0, a.act_p1);
   }
 #pragma unroll
   for (int j = 0; j < W; ++j) {
@@ -462,7 +462,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (a.swiglu) p[a.N + n] = u[j];
               if (n2_ok) p[n2] = u[j];
             } else {
-              float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
+              float v = a.swiglu ? pair_mul(a.swiglu, g[j], u[j], a.act_p0, a.act_p1) : g[j];
               st_dt(a.out, a.out_dt, row * a.ldo + n, epilogue_act(a.act, v + bias, a.act_p0, a.act_p1));
               if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
             }
@@ -485,8 +485,8 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
                                       long long ldo, float act_p0, float act_p1) {
   grid_dep_wait();
   grid_dep_launch();
-  const int act = swiglu >= 2 ? swiglu : 0;          // (the argument's codes: common.cuh)
-  swiglu = swiglu == NV_EPI_SWIGLU;
+  const int act = epi_unary(swiglu);                 // (the argument's codes: common.cuh)
+  swiglu = epi_pair(swiglu);
   const int width = swiglu ? 2 * N : N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)M_tok * N) return;
@@ -498,7 +498,7 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
     g += p[n];
     if (swiglu) u += p[N + n];
   }
-  float v = swiglu ? silu_mul(g, u) : g;
+  float v = swiglu ? pair_mul(swiglu, g, u, act_p0, act_p1) : g;
   if (bias) v += ld_dt(bias, bias_dt, n);
   st_dt(out, out_dt, t * ldo + n, epilogue_act(act, v, act_p0, act_p1));
 }
@@ -508,9 +508,11 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
 __global__ void tc_gemm_finish_grouped_kernel(const float* __restrict__ partial, int splits, int M_out, int N, int swiglu,
                                               const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                                               const int* __restrict__ num_tiles, void* __restrict__ out, int out_dt,
-                                              long long ldo) {
+                                              long long ldo, float act_p0, float act_p1) {
   grid_dep_wait();
   grid_dep_launch();
+  const int act = epi_unary(swiglu);
+  swiglu = epi_pair(swiglu);
   const int y = blockIdx.x;
   if (y >= *num_tiles) return;
   const int n = blockIdx.y * blockDim.x + threadIdx.x;
@@ -524,7 +526,7 @@ __global__ void tc_gemm_finish_grouped_kernel(const float* __restrict__ partial,
       g += p[n];
       if (swiglu) u += p[N + n];
     }
-    st_dt(out, out_dt, (long long)r * ldo + n, swiglu ? silu_mul(g, u) : g);
+    st_dt(out, out_dt, (long long)r * ldo + n, swiglu ? pair_mul(swiglu, g, u, act_p0, act_p1) : epilogue_act(act, g, act_p0, act_p1));
   }
 }
 
@@ -657,9 +659,8 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
-  const int act = swiglu >= 2 ? swiglu : 0;          // (see common.cuh: what the `swiglu` argument may say)
-  swiglu = swiglu == NV_EPI_SWIGLU;
-  if (act && tile_expert) return NV_ERR_UNSUPPORTED; // a unary activation: dense products only
+  const int act = epi_unary(swiglu);                 // (see common.cuh: what the `swiglu` argument may say)
+  swiglu = epi_pair(swiglu);
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
   if (M_tok <= 0 || N <= 0) return NV_OK;
   const bool grouped = tile_expert != nullptr;
@@ -682,7 +683,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.k_steps_total = (K + BLOCK_K - 1) / BLOCK_K;
   a.splits = splits < 1 ? 1 : splits;
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
-  a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0; a.act = act; a.act_p0 = act_p0; a.act_p1 = act_p1;
+  a.n_tile = n_tile; a.swiglu = swiglu; a.act = act; a.act_p0 = act_p0; a.act_p1 = act_p1;
   a.early = early ? 1 : 0;
   a.x_box = x_box;
   a.x_sub = x_sub; a.x_mod = x_mod;
@@ -773,8 +774,8 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   if (a.splits > 1) {
     if (grouped) {
       NV_RETURN_IF(launch_dep(tc_gemm_finish_grouped_kernel, dim3((unsigned)max_tiles, (unsigned)((N + 255) / 256)),
-                              dim3(256), 0, stream, (const float*)scratch, a.splits, a.M_out, N, a.swiglu, tile_row0,
-                              tile_rows, num_tiles, out, out_dt, ldo));
+                              dim3(256), 0, stream, (const float*)scratch, a.splits, a.M_out, N,
+                              a.act ? a.act : a.swiglu, tile_row0, tile_rows, num_tiles, out, out_dt, ldo, act_p0, act_p1));
     } else {
       const long long outputs = (long long)a.M_out * N;
       NV_RETURN_IF(launch_dep(tc_gemm_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream,

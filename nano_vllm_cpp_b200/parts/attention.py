@@ -42,6 +42,12 @@ class PagedAttention(Mixer):
     the whole value head): the value of position j is turned by j before it is stored, and a head's output at
     position i, the weighted sum of such values, is turned back by i, so that a value enters the output turned by
     ``j - i``.
+
+    Three more of the plain general path.  ``qk_norm_weight`` False: the head norm of q and k has no weight
+    tensors (a head is divided by its root mean square and nothing else).  ``qk_norm_after_rotation``: that norm
+    follows the turn instead of preceding it (with a position encoding whose cosines and sines carry an amplitude,
+    or that turns part of a head, the two orders differ).  ``score_softcap`` > 0: a scaled score s becomes
+    ``score_softcap * tanh(s / score_softcap)`` before mask and softmax.
     """
 
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -53,7 +59,8 @@ class PagedAttention(Mixer):
                  qk_norm_eps: float | None = None, out_bias: bool = False, sink_score: float | None = None,
                  names: dict | None = None, values_from_keys: bool = False, exact_weights: bool = False,
                  keep_first: int = 0, learned_sink: bool = False, head_mix: bool = False,
-                 value_position: PartSpec | None = None):
+                 value_position: PartSpec | None = None, qk_norm_weight: bool = True,
+                 qk_norm_after_rotation: bool = False, score_softcap: float = 0.0):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden, self.Hq, self.Hkv, self.D = hidden_size, num_heads, num_kv_heads, head_dim
@@ -65,6 +72,10 @@ class PagedAttention(Mixer):
         self.position = build_part("position", position) if isinstance(position, PartSpec) else position
         self.names = dict(self._NAMES, **(names or {}))
         self.values_from_keys = bool(values_from_keys)
+        self.qk_norm_weight, self.qk_norm_after = bool(qk_norm_weight), bool(qk_norm_after_rotation)
+        self.softcap = float(score_softcap)
+        if self.softcap < 0:
+            raise ValueError("score_softcap must not be negative")
         if self.values_from_keys and self.Dv != self.D:
             raise ValueError("values that are the keys have the keys' head size")
         if self.values_from_keys and bias:
@@ -84,7 +95,9 @@ class PagedAttention(Mixer):
                                  "values of their own")
         # the options that only the general kernels know, whatever the dtype
         self.extended = bool(self.keep_first or self.learned_sink or self.head_mix or self.value_position is not None)
-        self.general = (self.extended or self.values_from_keys or bool(exact_weights) or self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
+        if self.extended and self.softcap > 0:
+            raise ValueError("capped scores are not supported together with kept positions, learned sinks, mixed heads or turned values")
+        self.general = (self.extended or self.softcap > 0 or self.values_from_keys or bool(exact_weights) or self.Dv != self.D or self.qk_norm_eps is not None or self.sink_score is not None
                         or self.position.pairing != "halves" or self.position.amplitude != 1.0)
         if self.general:
             if self.extended:
@@ -109,7 +122,7 @@ class PagedAttention(Mixer):
                       n["v_bias"]: TensorSpec((vv,), kind="vector")})
         if self.out_bias:
             s[n["o_bias"]] = TensorSpec((H,), kind="vector")
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             s[n["q_norm"]] = TensorSpec((self.D,), init="ones", kind="vector")
             s[n["k_norm"]] = TensorSpec((self.D,), init="ones", kind="vector")
         if self.head_mix:
@@ -146,7 +159,7 @@ class PagedAttention(Mixer):
                 w[:, :, :self.Dv] = self.o_weight.view(self.hidden, self.Hq, self.Dv)
                 self.o_weight = w.view(self.hidden, self.Hq * self.pad)
         self.q_norm = self.k_norm = None
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm, self.k_norm = fetch(n["q_norm"]), fetch(n["k_norm"])
 
     def cache_spec(self):
@@ -185,7 +198,8 @@ class PagedAttention(Mixer):
         ops.qk_prepare_store(proj, 0, Hq * D, Hq * D if self.values_from_keys else (Hq + Hkv) * D, batch.positions, batch.row_entry, bt, self.q_norm,
                              self.k_norm, self.qk_norm_eps or 0.0, pos.inv_freq(), pos.rotary_dim,
                              pos.pairing == "interleaved", pos.amplitude, q, cache.k, cache.v, Hq, Hkv, D, Dv,
-                             cache.write, ctx.err)
+                             cache.write, ctx.err, norm_always=self.qk_norm_eps is not None,
+                             norm_after=self.qk_norm_after)
         att = torch.empty((T, Hq * (P or Dv)), dtype=ctx.act_dtype, device=h.device)
         if P:
             # Entries of one row go to the split-key decode kernel (with weights that keep their float32 bits), the
@@ -197,16 +211,17 @@ class PagedAttention(Mixer):
                 ops.attention_decode(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
                                      att, Hq, Hkv, P, batch.max_context if batch.decode_only else batch.max_single_context,
                                      rows=None if batch.decode_only else batch.single_rows, err=ctx.err,
-                                     sink_score=self.sink_score, float_weights=True)
+                                     sink_score=self.sink_score, float_weights=True, softcap=self.softcap)
             if single < batch.S:
                 tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
                 ops.attention_prefill(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
                                       self.window, att, Hq, Hkv, P, err=ctx.err, min_rows=2 if single else 1,
                                       kernel="mma" if self.sink_score is not None else "auto",
-                                      sink_score=self.sink_score, weight_terms=3)
+                                      sink_score=self.sink_score, weight_terms=3, softcap=self.softcap)
         else:
             ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
-                                        self.window, att, Hq, Hkv, D, Dv, sink_score=self.sink_score)
+                                        self.window, att, Hq, Hkv, D, Dv, sink_score=self.sink_score,
+                                        softcap=self.softcap)
         return linear(ctx, att, self.o_weight, torch.float32, bias=self.o_bias)
 
     def _forward_extended(self, proj, bt, batch, cache):

@@ -104,6 +104,7 @@ class Part:
 class Norm(Part):
     accepts_mix: bool = False        # True: ``forward`` takes a ``RowMix`` as the branch
     accepts_sum: bool = False        # True: ``forward`` takes a ``BranchSum`` as the branch
+    accepts_normed: bool = False     # True: ``forward`` takes a ``NormedBranch`` as the branch
 
     def forward(self, x, branch, want_f32: bool = False):
         raise NotImplementedError
@@ -145,6 +146,22 @@ class BranchSum:
 
 
 @dataclass
+class NormedBranch:
+    """A sublayer output that still has to pass a norm of its own before it is added to the residual stream:
+    ``x += norm.rms(branch) * norm.weight`` (the sublayers of a layer that norms every sublayer's input and output).
+    ``branch`` is a float32 matrix or a ``RowMix``.  A norm with ``accepts_normed`` does that sum and its own norm
+    of the stream in one kernel; for every other consumer ``resolve_branch`` lets ``norm`` add it first."""
+    branch: object
+    norm: object
+
+    def add_to(self, x) -> None:
+        y = self.branch
+        if isinstance(y, (RowMix, BranchSum)):
+            y = y.sum()
+        self.norm.add_normed(x, [y], want_rows=False)
+
+
+@dataclass
 class StreamRows:
     """What a layer hands on when nothing is left to add to the residual stream, but its rows already exist in the
     activation dtype (the layer's last kernel wrote them): a next layer that reads the stream itself takes them."""
@@ -155,6 +172,10 @@ def resolve_branch(norm: Norm, branch):
     """What ``norm.forward`` may be given for ``branch``: the mix itself if the norm sums it, else its sum."""
     if isinstance(branch, StreamRows):
         return None
+    if isinstance(branch, NormedBranch):
+        if getattr(norm, "accepts_normed", False):
+            return branch
+        raise TypeError("a branch that is normed before its sum needs a norm that takes it (RMSNorm)")
     if isinstance(branch, RowMix) and not norm.accepts_mix:
         return branch.sum()
     if isinstance(branch, BranchSum) and not getattr(norm, "accepts_sum", False):

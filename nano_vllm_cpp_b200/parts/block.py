@@ -14,7 +14,7 @@ feed-forward, a post-norm block) declares its own slots and is registered like a
 """
 from __future__ import annotations
 
-from .base import PartSpec, StreamRows, BranchSum, resolve_branch
+from .base import PartSpec, StreamRows, BranchSum, NormedBranch, resolve_branch
 from .registry import register_part, build_part
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "post_attention_layernorm.",
@@ -154,6 +154,36 @@ class BranchNormBlock(Arrangement):
 
 
 register_part("arrangement", "branch_norm", BranchNormBlock)
+
+
+class SandwichBlock(Arrangement):
+    """A norm before and after each sublayer: ``x += norm1b(mixer(norm1(x))); x += norm2b(feed_forward(norm2(x)))``.
+    A layer may have no feed-forward.  A sublayer's output is handed on as a ``NormedBranch``: the norm that runs
+    next (this layer's ``norm2``, the next layer's ``norm1`` or the model's last norm) norms it with the output
+    norm's weight, adds it to the stream and norms the stream for its own sublayer, all in one kernel."""
+    slots = {"norm1": "norm", "mixer": "mixer", "norm1b": "norm", "norm2": "norm", "feed_forward": "feed_forward",
+             "norm2b": "norm"}
+    optional = ("norm2", "feed_forward", "norm2b")
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        if len({self.norm2 is None, self.feed_forward is None, self.norm2b is None}) != 1:
+            raise ValueError("a sandwich layer's feed-forward comes with both of its norms")
+        for n in (self.norm1b, self.norm2b):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError("a sandwich layer's output norms must be able to norm a branch (RMSNorm)")
+
+    def forward(self, x, pending, batch, cache):
+        h, _ = self.norm1.forward(x, resolve_branch(self.norm1, pending))
+        pending = NormedBranch(self.mixer.forward(h, batch, cache), self.norm1b)
+        ff = self.feed_forward
+        if ff is None:
+            return pending
+        h, h32 = self.norm2.forward(x, resolve_branch(self.norm2, pending), want_f32=ff.wants_f32_input)
+        return NormedBranch(ff.forward(h, h32, batch), self.norm2b)
+
+
+register_part("arrangement", "sandwich", SandwichBlock)
 
 
 def build_layer(spec: LayerSpec):

@@ -20,24 +20,34 @@ MAX_ALIGNMENTS = 16
 
 
 class DenseSwiGLU(FeedForward):
-    """``down(silu(gate(h)) * up(h))`` (src/model.cpp:828-832; src/hip_ops.hip:419-429)."""
+    """``down(silu(gate(h)) * up(h))`` (src/model.cpp:828-832; src/hip_ops.hip:419-429).
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    ``clamp_limit`` > 0 makes the pairing of the two halves a clamped one instead, still in the first product's
+    epilogue: ``g = min(gate(h), limit)``, ``u = clamp(up(h), -limit, limit)``, ``down(g sigmoid(slope g) (u + 1))``.
+    ``names`` renames the tensors (keys: gate, up, down)."""
+
+    _NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    def __init__(self, hidden_size: int, intermediate_size: int, clamp_limit: float = 0.0, slope: float = 1.702,
+                 names: dict | None = None):
         self.hidden, self.inter = hidden_size, intermediate_size
+        if clamp_limit < 0:
+            raise ValueError("clamp_limit must not be negative")
+        self.pair = ("glu_clamped", float(clamp_limit), float(slope)) if clamp_limit > 0 else None
+        self.names = dict(self._NAMES, **(names or {}))
 
     def tensor_specs(self, available=None):
-        H, I = self.hidden, self.inter
-        return {"gate_proj.weight": TensorSpec((I, H)), "up_proj.weight": TensorSpec((I, H)),
-                "down_proj.weight": TensorSpec((H, I))}
+        H, I, n = self.hidden, self.inter, self.names
+        return {n["gate"]: TensorSpec((I, H)), n["up"]: TensorSpec((I, H)), n["down"]: TensorSpec((H, I))}
 
     def load(self, fetch, ctx):
         self.ctx = ctx
         # gate rows then up rows in one matrix (src/model.cpp:589-596)
-        self.gate_up = _cat([fetch("gate_proj.weight"), fetch("up_proj.weight")])
-        self.down = fetch("down_proj.weight")
+        self.gate_up = _cat([fetch(self.names["gate"]), fetch(self.names["up"])])
+        self.down = fetch(self.names["down"])
 
     def forward(self, h, h32, batch):
-        act = linear(self.ctx, h, self.gate_up, self.ctx.act_dtype, swiglu=True)
+        act = linear(self.ctx, h, self.gate_up, self.ctx.act_dtype, swiglu=True, act=self.pair)
         return linear(self.ctx, act, self.down, torch.float32)
 
 
@@ -106,6 +116,9 @@ class SparseMoeSwiGLU(FeedForward):
     gives the tensors' names where they are not the usual ones (keys: router, correction, shared_gate, and the
     patterns expert_gate, expert_up, expert_down with ``{}`` for the expert's number, shared_gate_proj, shared_up,
     shared_down).
+
+    ``expert_activation`` (one of ``ops.EPILOGUE_ACTS``, for instance ``relu2``): the experts, the shared one too,
+    have no gate matrix and are ``down(act(up(h)))``; the activation sits in the first product's epilogue.
     """
     wants_f32_input = True
 
@@ -117,7 +130,7 @@ class SparseMoeSwiGLU(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int,
                  shared_intermediate_size: int = 0, renormalize: bool = False, score: str = "softmax",
                  route_scale: float = 1.0, choice_bias: bool = False, shared_gate: bool = True,
-                 names: dict | None = None):
+                 names: dict | None = None, expert_activation: str | None = None):
         if not (1 <= top_k <= num_experts):
             raise ValueError("top_k must lie in 1..num_experts")
         if top_k > 32 or num_experts > 1536:
@@ -130,6 +143,10 @@ class SparseMoeSwiGLU(FeedForward):
             raise ValueError("a choice bias goes with sigmoid scores")
         self.score, self.route_scale, self.choice_bias = score, float(route_scale), bool(choice_bias)
         self.shared_gate = bool(shared_gate) and shared_intermediate_size > 0
+        if expert_activation is not None and expert_activation not in ops.EPILOGUE_ACTS:
+            raise ValueError(f"expert_activation must be one of {sorted(ops.EPILOGUE_ACTS)}, found {expert_activation!r}")
+        self.expert_act = expert_activation
+        self.gated = expert_activation is None          # SwiGLU experts: gate and up rows paired in the epilogue
         self.names = dict(self._NAMES, **(names or {}))
         self.rule = None                # what the routing kernels take beyond the softmax rule (set at load)
         self._align = {}
@@ -145,16 +162,18 @@ class SparseMoeSwiGLU(FeedForward):
         s = {n["router"]: TensorSpec((E, H))}
         if self.choice_bias:
             s[n["correction"]] = TensorSpec((E,), init="zeros", kind="vector")
-        if available is not None and available("experts.gate_up_proj"):  # stacked form, src/model.cpp:274-281
+        if self.gated and available is not None and available("experts.gate_up_proj"):  # stacked form, src/model.cpp:274-281
             s["experts.gate_up_proj"] = TensorSpec((E, 2 * I, H))
             s["experts.down_proj"] = TensorSpec((E, H, I))
         else:
             for e in range(E):
-                s[n["expert_gate"].format(e)] = TensorSpec((I, H))
+                if self.gated:
+                    s[n["expert_gate"].format(e)] = TensorSpec((I, H))
                 s[n["expert_up"].format(e)] = TensorSpec((I, H))
                 s[n["expert_down"].format(e)] = TensorSpec((H, I))
         if SI > 0:
-            s[n["shared_gate_proj"]] = TensorSpec((SI, H))
+            if self.gated:
+                s[n["shared_gate_proj"]] = TensorSpec((SI, H))
             s[n["shared_up"]] = TensorSpec((SI, H))
             s[n["shared_down"]] = TensorSpec((H, SI))
             if self.shared_gate:
@@ -168,8 +187,9 @@ class SparseMoeSwiGLU(FeedForward):
         bias = fetch(n["correction"]).float().contiguous() if self.choice_bias else None
         if self.score != "softmax" or bias is not None or self.route_scale != 1.0:
             self.rule = (self.score, bias, self.route_scale)
-        stacked = fetch.has("experts.gate_up_proj")
-        first = fetch("experts.gate_up_proj") if stacked else fetch(n["expert_gate"].format(0))
+        stacked = self.gated and fetch.has("experts.gate_up_proj")
+        G = 2 if self.gated else 1                       # matrices of an expert's first product
+        first = fetch("experts.gate_up_proj") if stacked else fetch(n["expert_gate" if self.gated else "expert_up"].format(0))
         # The shared expert as C more experts that every row visits: possible when its width is a whole
         # number of expert widths.  Its chunks then ride in the grouped products and need no launches of
         # their own.  Only the tensor-core path does this; the plain path keeps the shared expert apart.
@@ -178,19 +198,23 @@ class SparseMoeSwiGLU(FeedForward):
                              and H % 8 == 0 and I % 8 == 0) else 0
         EC = E + self.virtual
         # every expert's [gate; up] rows and down matrix in one block each, indexed by expert
-        self.w_gate_up = torch.empty((EC, 2 * I, H), dtype=first.dtype, device=first.device)
+        self.w_gate_up = torch.empty((EC, G * I, H), dtype=first.dtype, device=first.device)
         self.w_down = torch.empty((EC, H, I), dtype=first.dtype, device=first.device)
         if stacked:
             self.w_gate_up[:E].copy_(first)
             self.w_down[:E].copy_(fetch("experts.down_proj"))
         else:
             for e in range(E):
-                self.w_gate_up[e, :I].copy_(first if e == 0 else fetch(n["expert_gate"].format(e)))
-                self.w_gate_up[e, I:].copy_(fetch(n["expert_up"].format(e)))
+                if self.gated:
+                    self.w_gate_up[e, :I].copy_(first if e == 0 else fetch(n["expert_gate"].format(e)))
+                    self.w_gate_up[e, I:].copy_(fetch(n["expert_up"].format(e)))
+                else:
+                    self.w_gate_up[e].copy_(first if e == 0 else fetch(n["expert_up"].format(e)))
                 self.w_down[e].copy_(fetch(n["expert_down"].format(e)))
         del first
         if SI > 0:
-            sg, su = fetch(n["shared_gate_proj"]), fetch(n["shared_up"])
+            su = fetch(n["shared_up"])
+            sg = fetch(n["shared_gate_proj"]) if self.gated else su
             sd = fetch(n["shared_down"])
             self.sh_gate = fetch(n["shared_gate"]) if self.shared_gate else None
             # the gate's single row rides along with the router's rows: one product gives both logits
@@ -199,14 +223,17 @@ class SparseMoeSwiGLU(FeedForward):
             if (self.virtual and sg.dtype == su.dtype == sd.dtype == self.w_gate_up.dtype
                     and (self.router_and_gate is not None or not self.shared_gate)):
                 for c in range(self.virtual):
-                    self.w_gate_up[E + c, :I].copy_(sg[c * I:(c + 1) * I])
-                    self.w_gate_up[E + c, I:].copy_(su[c * I:(c + 1) * I])
+                    if self.gated:
+                        self.w_gate_up[E + c, :I].copy_(sg[c * I:(c + 1) * I])
+                        self.w_gate_up[E + c, I:].copy_(su[c * I:(c + 1) * I])
+                    else:
+                        self.w_gate_up[E + c].copy_(su[c * I:(c + 1) * I])
                     self.w_down[E + c].copy_(sd[:, c * I:(c + 1) * I])
             else:
                 if self.virtual:                       # mixed storage types: keep the shared expert apart
                     self.w_gate_up, self.w_down = self.w_gate_up[:E].clone(), self.w_down[:E].clone()
                     self.virtual = 0
-                self.sh_gate_up = _cat([sg, su])
+                self.sh_gate_up = _cat([sg, su]) if self.gated else su
                 self.sh_down = sd
         else:
             self.virtual = 0
@@ -268,15 +295,16 @@ class SparseMoeSwiGLU(FeedForward):
         self.last_alignment = al
         wide = al.secondary                      # the tile list of the SwiGLU product, if it has one of its own
         if x_sorted is not None:
-            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=True, tiles=wide, counter=c0)
+            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=self.gated, tiles=wide,
+                                 counter=c0, act=self.expert_act)
         else:
-            act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True,
-                                 tiles=wide, counter=c0)
+            act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=self.gated,
+                                 tiles=wide, counter=c0, act=self.expert_act)
         # the tile lists were final before the first product started: the second may start beside it
         y = grouped_linear(ctx, act, self.w_down, torch.float32, al, tiles_ready=True, counter=c1)
         shared = None
         if self.shared_inter > 0 and not C:
-            sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
+            sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=self.gated, act=self.expert_act)
             shared = linear(ctx, sact, self.sh_down, torch.float32)
             if gate_logit is None and self.shared_gate:
                 gate_logit = small_linear(ctx, h32, self.sh_gate)
@@ -309,8 +337,8 @@ class SparseMoeSwiGLU(FeedForward):
         side.wait_event(fork)
         cap = int(ops.num_sms() * SIDE_GRID_SHARE) if many else 0
         with torch.cuda.stream(side):
-            ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
-                                  x_rows=st.x_rows, max_ctas=cap)
+            ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=self.gated, err=ctx.err, tiles=st, tiles_ready=True,
+                                  x_rows=st.x_rows, max_ctas=cap, act=self.expert_act)
             ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
             join.record(side)
         # The routed products' CTAs take their tiles from a counter: a prompt's start while the side products still hold
@@ -332,7 +360,8 @@ class SparseMoeSwiGLU(FeedForward):
                                 zero=self._counters if c0 is not None else None, rule=self.rule)
         self.last_alignment = al
         x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
-        ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)
+        ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=self.gated, err=ctx.err, tiles_ready=True,
+                              counter=c0, act=self.expert_act)
         ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True, counter=c1)
         main.wait_event(join)
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, None, None)

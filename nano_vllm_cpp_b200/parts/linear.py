@@ -18,8 +18,10 @@ SKINNY_MAX_BYTES = 128 << 20
 
 def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None, out=None, act=None):
     """``out = a[a_rows] @ w.T (+ bias)``; with ``swiglu`` w is [2N, K] (gate rows, then up rows)
-    and ``out = silu(a @ gate.T) * (a @ up.T)``; with ``act`` (gelu_erf, gelu_tanh, silu) every value of the
-    result passes that function in the product's epilogue, on the float32 sum."""
+    and ``out = silu(a @ gate.T) * (a @ up.T)``; with ``act`` (gelu_erf, gelu_tanh, silu, relu2) every value of the
+    result passes that function in the product's epilogue, on the float32 sum; ``swiglu`` with
+    ``act=("glu_clamped", limit, slope)`` pairs the rows as ``g sigmoid(slope g) (u + 1)`` with ``g = min(gate, limit)``
+    and ``u = clamp(up, -limit, limit)``."""
     rows_w = w.shape[0]
     N = rows_w // 2 if swiglu else rows_w
     if M is None:
@@ -52,7 +54,7 @@ def small_linear(ctx, a32, w):
 
 
 def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None, tiles_ready=False, out=None,
-                   counter=None):
+                   counter=None, act=None):
     """Per-expert product over an expert-sorted row list: row r of the output belongs to the expert
     whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``.  ``counter``: see
     ``ops.gemm_fast_grouped`` (tensor-core path only)."""
@@ -64,7 +66,7 @@ def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, ti
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
         ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err, tiles=tiles,
-                              tiles_ready=tiles_ready, counter=counter)
+                              tiles_ready=tiles_ready, counter=counter, act=act)
     else:
-        ops.gemm_plain(a, w, out, a_rows=a_rows, swiglu=swiglu, M=align.TK, tiles=align.tiles)
+        ops.gemm_plain(a, w, out, a_rows=a_rows, swiglu=swiglu, M=align.TK, tiles=align.tiles, act=act)
     return out

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm, RowMix, BranchSum, TensorSpec
+from .base import Norm, RowMix, BranchSum, NormedBranch, TensorSpec
 from .registry import register_part
 
 
@@ -13,10 +13,12 @@ class RMSNorm(Norm):
 
     The residual stream and the statistics are float32; ``y`` is written in the activation dtype.
     A branch that is still a ``RowMix`` is summed by the same kernel, and so are the two outputs of a
-    ``BranchSum``.
+    ``BranchSum``.  A ``NormedBranch`` (a sublayer output with a norm of its own, ``n``) is taken in by one launch
+    that does both norms: ``x += rms_n(branch) * w_n; y = rms(x) * w``.
     """
     accepts_mix = True
     accepts_sum = True
+    accepts_normed = True
 
     def __init__(self, size: int, eps: float, weight_offset: float = 0.0, weight_name: str = "weight"):
         """``weight_offset``: the stored weight lies around zero and the multiplier is ``weight_offset`` + weight
@@ -53,6 +55,15 @@ class RMSNorm(Norm):
         if want_f32:
             out32 = out if out.dtype == torch.float32 else torch.empty_like(x)
         mix = branch2 = None
+        if isinstance(branch, NormedBranch):
+            inner, first = branch.branch, branch.norm
+            if isinstance(inner, RowMix) and inner.index.shape[1] <= ops.ADD_RMSNORM_MAX_MIX:
+                mix, inner = inner.as_tuple(), None
+            elif isinstance(inner, (RowMix, BranchSum)):
+                inner = inner.sum()
+            ops.branch_norm_add(x, [] if inner is None else [inner], first.weight, first.eps, out, mix=mix,
+                                next_weight=self.weight, next_eps=self.eps, out32=None if out32 is out else out32)
+            return out, out32
         if isinstance(branch, RowMix):
             if branch.index.shape[1] <= ops.ADD_RMSNORM_MAX_MIX:
                 mix, branch = branch.as_tuple(), None
