@@ -160,13 +160,19 @@ def relu2_expert(h, W, p):
 
 
 def route(h, W, p, top):
-    """(indices [T, top] in order of falling score, weights [T, top], the smallest gap between a chosen and the
-    best unchosen score per row)."""
-    s = torch.softmax(h @ W[p + "router"].T, dim=-1)
+    """(indices [T, top] in order of falling score, weights [T, top], and per row the gap between the last chosen
+    and the best unchosen router logit as a fraction of the spread of the row's logits: how near the row is to
+    choosing otherwise)."""
+    z = h @ W[p + "router"].T
+    s = torch.softmax(z, dim=-1)
     order = torch.argsort(s, dim=-1, descending=True, stable=True)
     idx = order[:, :top]
     w = torch.gather(s, 1, idx)
-    margin = (w[:, -1] - torch.gather(s, 1, order[:, top:top + 1])[:, 0]) if top < s.shape[1] else torch.full((h.shape[0],), 1.0, dtype=F64)
+    if top < s.shape[1]:
+        zs = torch.gather(z, 1, order)
+        margin = (zs[:, top - 1] - zs[:, top]) / (zs[:, 0] - zs[:, -1]).clamp_min(1e-30)
+    else:
+        margin = torch.full((h.shape[0],), 1.0, dtype=F64)
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20), margin
 
 
