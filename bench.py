@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design bizodra|kifunex|sanesun [--design-sizes s,m]     (another measurement, see ``design_bench``)
+    python bench.py --design bizodra|kifunex|sanesun|gekitar [--design-sizes s,m]     (another measurement, see ``design_bench``)
 
 Default run: the layer sizes of the Qwen1.5-MoE-A2.7B shape with random bfloat16 weights, a batch
 of 8 sequences each at a 2,048-token context; a step is one decode step of that batch.  ``value``
@@ -281,9 +281,44 @@ def sanesun_config(z):
             "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(z["layers"])]}
 
 
+# --design gekitar: the same measurement for the Gekitar decoder beside the closest existing model at equal size: a
+# Qwen2-MoE decoder (grouped-query attention around a mixture with a softmax router and a gated shared expert) with the
+# same width, depth, heads, head size, experts, experts per token, expert and shared-expert widths and vocabulary.
+# Gekitar's layers go latent attention, windowed latent attention, attention with capped scores and a sink, windowed
+# latent attention on the second layer's pages; three of four feed-forwards are mixtures, the fourth is dense with
+# the width that a token uses in a mixture.
+def gekitar_config(z):
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    rot = {"dims": 64, "base": 1e4}
+    latent = {"heads": H, "dim": D, "rot_dim": 64, "vdim": D, "q_rank": W // 2, "kv_rank": 192, "scale": (D + 64) ** -0.5,
+              "rot": rot}
+    windowed = dict(latent, mask={"size": z["window"]})
+    attn = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": 1.0, "softcap": 30.0,
+            "rot": {"dims": D, "base": 1e6, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    # (an expert here is two matrices where a SwiGLU expert is three: half as wide again gives it the same weights)
+    ff, shared_ff = z["ff"] * 3 // 2, z["shared_ff"] * 3 // 2
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": shared_ff}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"] + z["shared_ff"], "limit": 7.0}
+    layers = []
+    for i in range(z["layers"]):
+        k = i % 4
+        if k == 0:
+            layers.append({"type": "latent_attention", "mixer": latent, "mlp": moe})
+        elif k == 1:
+            layers.append({"type": "latent_attention_2", "mixer": windowed, "mlp": moe})
+        elif k == 2:
+            layers.append({"type": "attention", "mixer": attn, "mlp": moe})
+        else:
+            layers.append({"type": "latent_attention_2", "mixer": dict(windowed, kv_from=i - 2), "mlp": dense})
+    return {"architecture": "Gekitar", "vocab": z["vocab"], "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": layers}
+
+
 DESIGNS = {"bizodra": (DESIGN_SIZES, "bizodra", bizodra_config, "qwen2_dense", dense_qwen_config),
            "kifunex": (KIFUNEX_SIZES, "kifunex", kifunex_config, "qwen2_moe", sparse_qwen_config),
-           "sanesun": (DESIGN_SIZES, "sanesun", sanesun_config, "bizodra", bizodra_config)}
+           "sanesun": (DESIGN_SIZES, "sanesun", sanesun_config, "bizodra", bizodra_config),
+           "gekitar": (KIFUNEX_SIZES, "gekitar", gekitar_config, "qwen2_moe", sparse_qwen_config)}
 
 
 def design_bench(args) -> int:
