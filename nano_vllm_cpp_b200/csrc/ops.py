@@ -1325,7 +1325,7 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         out.stride(0), _epilogue(swiglu, act), n_tile, splits,
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), 0, 0,
                         _p(err.t if err is not None else _global_err().t), _early(), 0, 0,
-                        0, _p(None), 0, *_act_numbers(act), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+                        0, _p(None), 0, *_act_numbers(act), 0, 0, 0, _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
            w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
@@ -1371,8 +1371,52 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), tl.max_tiles,
                             rows_w, _p(err.t if err is not None else _global_err().t),
                             (_early() if tiles_ready else 0), x_sub, x_mod, max_ctas,
-                            _p(counter), align.TK, *_act_numbers(act), _stream()),
+                            _p(counter), align.TK, *_act_numbers(act), 0, 0, 0, _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
+
+
+class HeadTiles:
+    """The fixed tile list of a product per head over ``T`` rows that hold their ``H`` heads side by side: one tile
+    per (token tile, head), the heads of a token tile next to one another so that the CTAs that run together read
+    the same rows."""
+
+    def __init__(self, T: int, H: int, device, tile_m: int = 128):
+        self.T, self.H, self.tile_m = T, H, tile_m
+        heads, row0, rows = [], [], []
+        for r in range(0, T, tile_m):
+            for h in range(H):
+                heads.append(h)
+                row0.append(r)
+                rows.append(min(tile_m, T - r))
+        i32 = dict(dtype=torch.int32, device=device)
+        self.max_tiles = len(heads)
+        self.tile_expert = torch.tensor(heads, **i32)
+        self.tile_row0 = torch.tensor(row0, **i32)
+        self.tile_rows = torch.tensor(rows, **i32)
+        self.num_tiles = torch.tensor([len(heads)], **i32)
+
+
+def gemm_fast_heads_usable(x, w, out, K: int) -> bool:
+    return bool(_tma_ok(x) and _tma_ok(w) and w.is_contiguous() and K % 8 == 0 and out.dtype in _DT
+                and out.stride(-1) == 1 and x.shape[0] > 0)
+
+
+def gemm_fast_heads(x, w, out, tiles: HeadTiles, x_step: int, o_step: int, err=None) -> None:
+    """``out[t, h * o_step + n] = sum_k x[t, h * x_step + k] * w[h, n, k]`` for k < K = ``w.shape[2]``: one product per
+    head on the tensor cores in a single launch, over bfloat16 rows that hold their heads side by side (``x_step``
+    columns apart; a head's K columns may be the first of its block).  ``w`` is [H, N, K]; ``tiles``: a ``HeadTiles``
+    for these rows."""
+    H, N, K = w.shape
+    T = x.shape[0]
+    _need(gemm_fast_heads_usable(x, w, out, K) and tiles.T == T and tiles.H == H, "per-head product: operands")
+    _need(x_step % 8 == 0 and x.shape[1] >= (H - 1) * x_step + K and out.shape[0] >= T
+          and out.shape[1] >= (H - 1) * o_step + N, "per-head product: shapes")
+    _check(lib().nv_tc_gemm(_p(x), x.stride(0), T, _p(w), H * N, N, K, _p(None), 0, _p(out), dt(out), out.stride(0),
+                            0, tiles.tile_m, 1, _p(None), _p(tiles.tile_expert), _p(tiles.tile_row0),
+                            _p(tiles.tile_rows), _p(tiles.num_tiles), tiles.max_tiles, N,
+                            _p(err.t if err is not None else _global_err().t), 0, 0, 0, 0, _p(None), T, 0.0, 0.0,
+                            x_step, o_step, x.shape[1], _stream()),
+           f"tc_gemm_heads N={N} K={K}", 2.0 * T * H * N * K)
 
 
 _dependent_launch = 1

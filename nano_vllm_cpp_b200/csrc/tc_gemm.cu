@@ -73,6 +73,11 @@ struct TcArgs {
   // Grouped products whose tiles' tokens are not rows row0.. of X but rows (row0 - x_sub) mod x_mod.. of it
   // (x_mod > 0): several experts that all take the same rows of a short X, outputs one segment after the other.
   int x_sub, x_mod;
+  // Grouped products over column blocks (x_col_step > 0 or o_col_step > 0): a tile of "expert" e reads its tokens'
+  // columns e * x_col_step .. of X and writes columns e * o_col_step .. of the output, its rows being the tokens'
+  // own: a product per head of rows that hold their heads side by side.  (Columns that a k-step reads beyond the
+  // head's own meet the zeros that the weight map fills in beyond K.)
+  int x_col_step, o_col_step;
   // Tiles handed out by a counter instead of by position (nullptr: CTA b takes tiles b, b + grid, ...): a CTA that
   // starts late, because another kernel still holds its multiprocessor, then takes fewer tiles, and CTAs whose tiles
   // are short take more.  The counter must be 0 at launch; the CTA that draws the last number sets it back to 0.
@@ -86,7 +91,7 @@ struct TcArgs {
 // ring and the barriers' phases run on across tiles, and the accumulator is double-buffered in
 // TMEM (when two fit), so the epilogue of one tile overlaps the products of the next.
 struct Tile {
-  int nb, row0, x_row0, rows_here, w_row_base, z, n_steps, k_begin;
+  int nb, row0, x_row0, rows_here, w_row_base, z, n_steps, k_begin, x_col0, o_col0;
 };
 
 __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_tiles, Tile& t) {
@@ -107,7 +112,10 @@ __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_til
     t.rows_here = a.tile_rows[y];
     t.w_row_base = a.tile_expert[y] * a.rows_per_expert;
     t.x_row0 = a.x_mod ? (t.row0 - a.x_sub) % a.x_mod : t.row0;
+    t.x_col0 = a.tile_expert[y] * a.x_col_step;
+    t.o_col0 = a.tile_expert[y] * a.o_col_step;
   } else {
+    t.x_col0 = t.o_col0 = 0;
     t.row0 = y * a.n_tile;
     t.rows_here = min(a.n_tile, a.M_tok - t.row0);
     t.w_row_base = 0;
@@ -127,6 +135,15 @@ __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_til
 // accumulator sets, the second set's: the up rows of a SwiGLU, or feature n2 of a dual tile): both sets' loads from
 // tensor memory are in flight together, all values are worked out before the first store, and a whole chunk is
 // stored without a test per element, so that the one warp a scheduler has for this overlaps its own latencies.
+template <int W, int ACT>
+__device__ __forceinline__ void chunk_act(float (&g)[W], float (&u)[W], float p0, float p1) {
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    g[j] = epilogue_act(ACT, g[j], p0, p1);
+    u[j] = epilogue_act(ACT, u[j], p0, p1);
+  }
+}
+
 template <int W>
 __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, int two, uint32_t taddr, int c0, int n,
                                                int n2, bool n_ok, bool n2_ok, float bias, float bias2) {
@@ -172,8 +189,8 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
     for (int j = 0; j < W; ++j) {
       if (j < valid) {
         const float v = (a.swiglu ? pair_mul(a.swiglu, g[j], u[j], a.act_p0, a.act_p1) : g[j]) + bias;
-        st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, epilogue_act(a.act, v, a.act_p0, a.act_p1));
-        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
+        st_dt(a.out, a.out_dt, (row + j) * a.ldo + t.o_col0 + n, epilogue_act(a.act, v, a.act_p0, a.act_p1));
+        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + t.o_col0 + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
       }
     }
     return;
@@ -187,15 +204,19 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
     g[j] += bias;
     u[j] += bias2;
   }
-  if (a.act) {
-#pragma unroll
-    for (int j = 0; j < W; ++j) {
-      g[j] = epilogue_act(a.act, g[j], a.act_p0, a.act_p1);
-      u[j] = epilogue_act(a.act, u[j], a.act_p0, a.act_p1);
-    }
+  // (the activation's code is fixed per case, so that each case is one unrolled run of its own arithmetic: with
+  // the code tested per value the loop over a chunk kept its branches, and a squared relu cost the product of a
+  // prompt 0.37 instead of 0.15 ms)
+  switch (a.act) {
+    case 0: break;
+    case NV_EPI_GELU_ERF: chunk_act<W, NV_EPI_GELU_ERF>(g, u, a.act_p0, a.act_p1); break;
+    case NV_EPI_GELU_TANH: chunk_act<W, NV_EPI_GELU_TANH>(g, u, a.act_p0, a.act_p1); break;
+    case NV_EPI_SILU: chunk_act<W, NV_EPI_SILU>(g, u, a.act_p0, a.act_p1); break;
+    case NV_EPI_XIELU: chunk_act<W, NV_EPI_XIELU>(g, u, a.act_p0, a.act_p1); break;
+    default: chunk_act<W, NV_EPI_RELU2>(g, u, a.act_p0, a.act_p1); break;
   }
   if (a.out_dt == NV_DT_BF16) {
-    bf16* o = (bf16*)a.out + row * a.ldo;
+    bf16* o = (bf16*)a.out + row * a.ldo + t.o_col0;
 #pragma unroll
     for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n] = __float2bfloat16_rn(g[j]);
     if (n2_ok) {
@@ -203,7 +224,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
       for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n2] = __float2bfloat16_rn(u[j]);
     }
   } else {
-    float* o = (float*)a.out + row * a.ldo;
+    float* o = (float*)a.out + row * a.ldo + t.o_col0;
 #pragma unroll
     for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n] = g[j];
     if (n2_ok) {
@@ -318,7 +339,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
           if (tokens)
             for (int b = 0; b < boxes; ++b)
-              tma_load_2d_a(st + a_bytes * (two ? 2 : 1) + (uint32_t)b * a.x_box * 128, &tm_x, bar, kc,
+              tma_load_2d_a(st + a_bytes * (two ? 2 : 1) + (uint32_t)b * a.x_box * 128, &tm_x, bar, kc + t.x_col0,
                             t.x_row0 + b * a.x_box);
         }
       };
@@ -463,8 +484,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (n2_ok) p[n2] = u[j];
             } else {
               float v = a.swiglu ? pair_mul(a.swiglu, g[j], u[j], a.act_p0, a.act_p1) : g[j];
-              st_dt(a.out, a.out_dt, row * a.ldo + n, epilogue_act(a.act, v + bias, a.act_p0, a.act_p1));
-              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
+              st_dt(a.out, a.out_dt, row * a.ldo + t.o_col0 + n, epilogue_act(a.act, v + bias, a.act_p0, a.act_p1));
+              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + t.o_col0 + n2, epilogue_act(a.act, u[j] + bias2, a.act_p0, a.act_p1));
             }
           }
         }
@@ -655,8 +676,12 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
                       int early, int x_sub, int x_mod, int max_ctas, int* tile_counter, int m_out,
-                      float act_p0, float act_p1, cudaStream_t stream) {
+                      float act_p0, float act_p1, int x_col_step, int o_col_step, int x_cols, cudaStream_t stream) {
+  // x_col_step / o_col_step (grouped products only): see TcArgs; x_cols: the columns that a row of X holds then (K is
+  // the columns of one block).  Such a product does not split K, and its steps are 8 columns aligned.
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
+  if (x_col_step < 0 || o_col_step < 0 || x_col_step % 8) return NV_ERR_BAD_SIZE;
+  if ((x_col_step || o_col_step) && (!tile_expert || splits > 1 || x_mod || x_cols < K)) return NV_ERR_BAD_SIZE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (swiglu < 0 || swiglu > NV_EPI_LAST) return NV_ERR_BAD_SIZE;
   const int act = epi_unary(swiglu);                 // (see common.cuh: what the `swiglu` argument may say)
@@ -672,7 +697,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   int rc = get_map(W, w_rows_total, K, K, TILE_W, &tm_w);
   if (rc) return rc;
   const int x_box = n_tile < 64 ? n_tile : 64;
-  rc = get_map(X, M_tok, K, ldx, x_box, &tm_x);
+  rc = get_map(X, M_tok, x_col_step ? x_cols : K, ldx, x_box, &tm_x);
   if (rc) return rc;
 
   TcArgs a;
@@ -687,6 +712,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.early = early ? 1 : 0;
   a.x_box = x_box;
   a.x_sub = x_sub; a.x_mod = x_mod;
+  a.x_col_step = x_col_step; a.o_col_step = o_col_step;
   a.tile_counter = tile_counter;
   // Many tokens per tile and enough features: two weight tiles per CTA.  The operands then cost 2*16 KB + X
   // per k-step for twice the flops, which is what the shared-memory fill rate, the limit here, rewards.

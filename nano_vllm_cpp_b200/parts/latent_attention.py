@@ -111,13 +111,28 @@ class LatentAttention(Mixer):
         self.w_uv = torch.zeros((H, P, Dv), dtype=uv.dtype, device=uv.device)
         self.w_uv[:, :rk, :] = uv.transpose(1, 2)
         self.w_out = fetch(n["o"])
-        # A bfloat16 run with many rows makes the two small products per head on the tensor cores, head by head
-        # on views of the rows: the weights as [out, in] per head.
+        # A bfloat16 run with many rows makes the two small products per head on the tensor cores, all heads in one
+        # launch (``ops.gemm_fast_heads``: a tile per token tile and head): the weights as [out, in] per head.
+        self._tiles, self._tiles_kept = {}, set()
         self.tc_heads = (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and uk.dtype == torch.bfloat16
                          and (D + R) % 8 == 0 and Dv % 8 == 0 and rk % 8 == 0 and P % 8 == 0)
         if self.tc_heads:
             self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()                     # [h][r][d]
             self.w_uv_n = uv.contiguous()                                            # [h][v][r] over the latent's part of a row
+
+    def _head_tiles(self, T, dev):
+        """The tile list of the per-head products for a step of T rows; lists made while a step is captured are
+        named by address in its graph and stay."""
+        key = (T, torch.device(dev))
+        tl = self._tiles.get(key)
+        if tl is None:
+            loose = [k for k in self._tiles if k not in self._tiles_kept]
+            if len(loose) >= 64:
+                self._tiles.pop(loose[0])
+            tl = self._tiles[key] = ops.HeadTiles(T, self.H, dev)
+        if torch.cuda.is_current_stream_capturing():
+            self._tiles_kept.add(key)
+        return tl
 
     def cache_spec(self):
         return KVCacheSpec(1, self.P, self.cache_window, 0, 0, values=False)
@@ -157,8 +172,8 @@ class LatentAttention(Mixer):
         else:
             q = linear(ctx, cq, self.w_uq, torch.bfloat16 if tc else torch.float32)
         if tc:
-            for hd in range(H):
-                linear(ctx, q[:, hd * (D + R):(hd + 1) * (D + R)], self.w_uk_t[hd], mid, out=q_lat[:, hd * P:(hd + 1) * P])
+            head_tiles = self._head_tiles(T, dev)
+            ops.gemm_fast_heads(q, self.w_uk_t, q_lat, head_tiles, D + R, P, err=ctx.err)
         else:
             ops.head_project(q, self.w_uk, q_lat, H, D + R, P)
         lat = torch.empty((T, H * P), dtype=mid, device=dev)
@@ -181,8 +196,7 @@ class LatentAttention(Mixer):
         o = torch.empty((T, H * Dv), dtype=ctx.act_dtype, device=dev)
         if tc:
             o32 = torch.empty((T, H * Dv), dtype=torch.float32, device=dev) if self.output_gate else o
-            for hd in range(H):
-                linear(ctx, lat[:, hd * P:hd * P + rk], self.w_uv_n[hd], o32.dtype, out=o32[:, hd * Dv:(hd + 1) * Dv])
+            ops.gemm_fast_heads(lat, self.w_uv_n, o32, head_tiles, P, Dv, err=ctx.err)      # (the latent's part of every row)
             if self.output_gate:
                 ops.head_gate(o32, down, self.gate_col, o, H, Dv, gate_each=self.gate_each)
         else:
