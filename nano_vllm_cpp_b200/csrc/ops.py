@@ -264,13 +264,20 @@ def embedding(ids, table, out, err: ErrorFlag, feed=None, copies: int = 1, scale
                               float(scale), _p(err.t), _stream()), "embedding")
 
 
-def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None, branch2=None) -> None:
+def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None, branch2=None, branch_weight=None,
+                branch_eps: float = 0.0) -> None:
     """x (+= branch (+ branch2)); out = rmsnorm(x) * w; optional float32 copy of out.
 
     ``mix`` = (rows, index, weight, dense, gate_logit) gives the branch as a sum that has not been taken yet:
     ``sigmoid(gate_logit[t]) * dense[t] + sum_r weight[t, r] * rows[index[t, r]]`` (dense and gate_logit may be
-    None); it is summed inside the kernel instead of by ``moe_combine`` first."""
-    _cuda_contig(x, branch, branch2, w, out, out32)
+    None); it is summed inside the kernel instead of by ``moe_combine`` first.
+
+    ``branch_weight`` (float32 [H]): the branch, in whichever form, passes an RMS norm of its own first,
+    ``x += rms(branch) * branch_weight`` with ``branch_eps`` inside its root, in the same pass over the row."""
+    _cuda_contig(x, branch, branch2, w, out, out32, branch_weight)
+    _need(branch_weight is None or (branch_weight.dtype == torch.float32 and branch_weight.numel() == x.shape[1]
+                                    and (branch is not None or mix is not None)),
+          "add_rmsnorm: a branch weight is float32 [H] and comes with a branch")
     T, H = x.shape
     _need(x.dtype == torch.float32, "add_rmsnorm: the residual stream is float32")
     _need(branch2 is None or (branch is not None and branch2.dtype == torch.float32 and branch2.shape == x.shape),
@@ -299,7 +306,7 @@ def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None, branch2=
             _need(t_ is None or t_.data_ptr() % 16 == 0, "add_rmsnorm: rows must start on 16-byte boundaries")
     _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(branch2), _p(w), dt(w), eps, _p(out), dt(out),
                                 _p(out32), T, H, _p(rows), _p(index), _p(weight), R, _p(dense),
-                                _p(gate), gate_ld, _stream()), "add_rmsnorm")
+                                _p(gate), gate_ld, _p(branch_weight), float(branch_eps), _stream()), "add_rmsnorm")
 
 
 ADD_RMSNORM_MAX_MIX = 64

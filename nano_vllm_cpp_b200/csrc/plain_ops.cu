@@ -62,6 +62,11 @@ struct NormArgs {
   long long gate_ld;
   float eps;
   int w_dt, out_dt, H, R;
+  // The branch passes an RMS norm of its own before it is added (NORMED kernels): x += rms(branch) * bw, with b_eps
+  // inside its root; then the norm of the stream as always.  (A layer that norms a sublayer's output as well as
+  // its input: both norms in one pass over the row.)
+  const float* bw;
+  float b_eps;
 };
 
 template <int VEC>
@@ -88,7 +93,7 @@ __device__ __forceinline__ void st_chunk(float* p, const Chunk<VEC>& c) {
   }
 }
 
-template <int VEC>
+template <int VEC, bool NORMED = false>
 __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
   __shared__ float red[NORM_THREADS / 32];
   __shared__ int s_idx[NORM_MAX_R];
@@ -109,50 +114,90 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
   if (a.dense && a.gate_logit) gate = 1.f / (1.f + expf(-a.gate_logit[(size_t)t * a.gate_ld]));
   const bool adds = a.branch || a.R > 0 || a.dense;
 
-  // value of the updated residual stream at chunk c (and its write-back when something was added)
-  auto updated = [&](int c) {
-    Chunk<VEC> v = ld_chunk<VEC>(a.x + base + (size_t)c * VEC);
+  // the branch at chunk c: the matrix (or the two), or the weighted rows with the gated dense term
+  auto branch_at = [&](int c) {
+    Chunk<VEC> r;
     if (a.branch) {
-      Chunk<VEC> b = ld_chunk<VEC>(a.branch + base + (size_t)c * VEC);
+      r = ld_chunk<VEC>(a.branch + base + (size_t)c * VEC);
       if (a.branch2) {          // x + (b + b2): the branches are summed first
         Chunk<VEC> b2 = ld_chunk<VEC>(a.branch2 + base + (size_t)c * VEC);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) b.v[j] += b2.v[j];
+        for (int j = 0; j < VEC; ++j) r.v[j] += b2.v[j];
+      }
+      return r;
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) r.v[j] = 0.f;
+    // four rows' loads are in flight before the first is used; the sum keeps the order of k
+    int k = 0;
+    for (; k + 4 <= a.R; k += 4) {
+      Chunk<VEC> y[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) y[u] = ld_chunk<VEC>(a.rows + (size_t)s_idx[k + u] * a.H + (size_t)c * VEC);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float wk = s_w[k + u];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) r.v[j] = fmaf(wk, y[u].v[j], r.v[j]);
+      }
+    }
+    for (; k < a.R; ++k) {
+      Chunk<VEC> y = ld_chunk<VEC>(a.rows + (size_t)s_idx[k] * a.H + (size_t)c * VEC);
+      const float wk = s_w[k];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) r.v[j] = fmaf(wk, y.v[j], r.v[j]);
+    }
+    if (a.dense) {
+      Chunk<VEC> d = ld_chunk<VEC>(a.dense + base + (size_t)c * VEC);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) r.v[j] = d.v[j] * gate + r.v[j];
+    }
+    return r;
+  };
+
+  // NORMED: the branch's own norm first.  Its chunks stay in registers between the passes, as the stream's do.
+  Chunk<VEC> ykeep[NORMED ? NORM_CACHE : 1];
+  float rb = 1.f;
+  if (NORMED) {
+    float sy = 0.f;
+#pragma unroll
+    for (int u = 0; u < NORM_CACHE; ++u) {
+      const int c = tid + u * NORM_THREADS;
+      if (c < chunks) {
+        ykeep[NORMED ? u : 0] = branch_at(c);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) sy = fmaf(ykeep[NORMED ? u : 0].v[j], ykeep[NORMED ? u : 0].v[j], sy);
+      }
+    }
+    for (int c = tid + NORM_CACHE * NORM_THREADS; c < chunks; c += NORM_THREADS) {
+      Chunk<VEC> y = branch_at(c);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) sy = fmaf(y.v[j], y.v[j], sy);
+    }
+    sy = warp_sum(sy);
+    if ((tid & 31) == 0) red[tid >> 5] = sy;
+    __syncthreads();
+    float ty = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_THREADS / 32; ++i) ty += red[i];
+    rb = rsqrtf(ty / (float)a.H + a.b_eps);
+    __syncthreads();            // (red is written again below)
+  }
+
+  // value of the updated residual stream at chunk c (and its write-back when something was added); `y`: the branch's
+  // chunk where it was kept
+  auto updated = [&](int c, const Chunk<VEC>* y) {
+    Chunk<VEC> v = ld_chunk<VEC>(a.x + base + (size_t)c * VEC);
+    if (adds) {
+      Chunk<VEC> b = y ? *y : branch_at(c);
+      if (NORMED) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) b.v[j] = b.v[j] * rb * a.bw[(size_t)c * VEC + j];
       }
 #pragma unroll
       for (int j = 0; j < VEC; ++j) v.v[j] += b.v[j];
-    } else if (a.R > 0 || a.dense) {
-      Chunk<VEC> r;
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) r.v[j] = 0.f;
-      // four rows' loads are in flight before the first is used; the sum keeps the order of k
-      int k = 0;
-      for (; k + 4 <= a.R; k += 4) {
-        Chunk<VEC> y[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) y[u] = ld_chunk<VEC>(a.rows + (size_t)s_idx[k + u] * a.H + (size_t)c * VEC);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float wk = s_w[k + u];
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) r.v[j] = fmaf(wk, y[u].v[j], r.v[j]);
-        }
-      }
-      for (; k < a.R; ++k) {
-        Chunk<VEC> y = ld_chunk<VEC>(a.rows + (size_t)s_idx[k] * a.H + (size_t)c * VEC);
-        const float wk = s_w[k];
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) r.v[j] = fmaf(wk, y.v[j], r.v[j]);
-      }
-      if (a.dense) {
-        Chunk<VEC> d = ld_chunk<VEC>(a.dense + base + (size_t)c * VEC);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) r.v[j] = d.v[j] * gate + r.v[j];
-      }
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) v.v[j] += r.v[j];
+      st_chunk<VEC>(a.x + base + (size_t)c * VEC, v);
     }
-    if (adds) st_chunk<VEC>(a.x + base + (size_t)c * VEC, v);
     return v;
   };
 
@@ -162,13 +207,13 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
   for (int u = 0; u < NORM_CACHE; ++u) {
     const int c = tid + u * NORM_THREADS;
     if (c < chunks) {
-      keep[u] = updated(c);
+      keep[u] = updated(c, NORMED ? &ykeep[NORMED ? u : 0] : nullptr);
 #pragma unroll
       for (int j = 0; j < VEC; ++j) ss = fmaf(keep[u].v[j], keep[u].v[j], ss);
     }
   }
   for (int c = tid + NORM_CACHE * NORM_THREADS; c < chunks; c += NORM_THREADS) {
-    Chunk<VEC> v = updated(c);
+    Chunk<VEC> v = updated(c, nullptr);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) ss = fmaf(v.v[j], v.v[j], ss);
   }
@@ -577,8 +622,10 @@ NV_API int nv_embedding(const int* ids, const int* feed, const void* table, int 
 NV_API int nv_add_rmsnorm(float* x, const float* branch, const float* branch2, const void* w, int w_dt, float eps, void* out,
                           int out_dt, float* out32, int T, int H, const float* rows, const int* index,
                           const float* weight, int R, const float* dense, const float* gate_logit,
-                          long long gate_ld, cudaStream_t s) {
+                          long long gate_ld, const float* branch_w, float branch_eps, cudaStream_t s) {
+  // branch_w: the branch passes an RMS norm with this weight (and branch_eps) before it is added
   if (!dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (branch_w && !(branch || R > 0 || dense)) return NV_ERR_BAD_SIZE;
   if (R < 0 || R > NORM_MAX_R || (R > 0 && (!rows || !index || !weight))) return NV_ERR_BAD_SIZE;
   if (branch && (R > 0 || dense)) return NV_ERR_BAD_SIZE;   // one form of the branch at a time
   if (branch2 && !branch) return NV_ERR_BAD_SIZE;
@@ -587,6 +634,12 @@ NV_API int nv_add_rmsnorm(float* x, const float* branch, const float* branch2, c
   a.x = x; a.branch = branch; a.branch2 = branch2; a.w = w; a.out = out; a.out32 = out32; a.rows = rows; a.index = index;
   a.weight = weight; a.dense = dense; a.gate_logit = gate_logit; a.gate_ld = gate_ld; a.eps = eps;
   a.w_dt = w_dt; a.out_dt = out_dt; a.H = H; a.R = R;
+  a.bw = branch_w; a.b_eps = branch_eps;
+  if (branch_w) {
+    if (H % 4 == 0) NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<4, true>, dim3(T), dim3(NORM_THREADS), 0, s, a));
+    else NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<1, true>, dim3(T), dim3(NORM_THREADS), 0, s, a));
+    NV_RETURN_LAST();
+  }
   if (H % 4 == 0) NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<4>, dim3(T), dim3(NORM_THREADS), 0, s, a));
   else NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<1>, dim3(T), dim3(NORM_THREADS), 0, s, a));
   NV_RETURN_LAST();

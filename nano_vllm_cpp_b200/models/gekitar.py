@@ -47,7 +47,7 @@ def _mixer(cfg: GekitarConfig, i: int) -> PartSpec:
             hidden_size=W, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, v_head_dim=m.vdim, bias=True,
             out_bias=True, scale=m.scale, position=_rotation(m.rot_dims, m.rot_base, m.rot_scaling), qk_norm_eps=eps,
             qk_norm_weight=False, qk_norm_after_rotation=True, score_softcap=m.softcap, sink_score=0.0,
-            exact_weights=True, names=names))
+            round_weights=True, names=names))
     if isinstance(m, LatentConfig):
         # the pages of a layer that others read are kept for the longest window among their readers
         windows = [m.window] + [L.mixer.window for L in cfg.layers
@@ -57,7 +57,7 @@ def _mixer(cfg: GekitarConfig, i: int) -> PartSpec:
             hidden_size=W, heads=m.heads, dim=m.dim, vdim=m.vdim, q_rank=m.q_rank, kv_rank=m.kv_rank, scale=m.scale,
             eps=eps, output_gate=m.gated, gate_each=True, rot_dim=m.rot_dim,
             position=_rotation(m.rot_dim, m.rot_base, m.rot_scaling) if m.rot_dim else None, window=m.window,
-            cache_window=keep, own_kv=m.kv_from is None))
+            cache_window=keep, own_kv=m.kv_from is None, exact_weights=False))
     raise TypeError(type(m))
 
 

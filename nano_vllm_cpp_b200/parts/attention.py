@@ -47,7 +47,9 @@ class PagedAttention(Mixer):
     tensors (a head is divided by its root mean square and nothing else).  ``qk_norm_after_rotation``: that norm
     follows the turn instead of preceding it (with a position encoding whose cosines and sines carry an amplitude,
     or that turns part of a head, the two orders differ).  ``score_softcap`` > 0: a scaled score s becomes
-    ``score_softcap * tanh(s / score_softcap)`` before mask and softmax.
+    ``score_softcap * tanh(s / score_softcap)`` before mask and softmax.  ``round_weights``: a bfloat16 run of
+    this path rounds the softmax weights (computed in float32) to bfloat16 for their product with the values, as it
+    rounds every other operand of a product, instead of taking them in as three bfloat16 terms.
     """
 
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -60,7 +62,7 @@ class PagedAttention(Mixer):
                  names: dict | None = None, values_from_keys: bool = False, exact_weights: bool = False,
                  keep_first: int = 0, learned_sink: bool = False, head_mix: bool = False,
                  value_position: PartSpec | None = None, qk_norm_weight: bool = True,
-                 qk_norm_after_rotation: bool = False, score_softcap: float = 0.0):
+                 qk_norm_after_rotation: bool = False, score_softcap: float = 0.0, round_weights: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden, self.Hq, self.Hkv, self.D = hidden_size, num_heads, num_kv_heads, head_dim
@@ -74,6 +76,7 @@ class PagedAttention(Mixer):
         self.values_from_keys = bool(values_from_keys)
         self.qk_norm_weight, self.qk_norm_after = bool(qk_norm_weight), bool(qk_norm_after_rotation)
         self.softcap = float(score_softcap)
+        self.weight_terms = 1 if round_weights else 3
         if self.softcap < 0:
             raise ValueError("score_softcap must not be negative")
         if self.values_from_keys and self.Dv != self.D:
@@ -211,13 +214,14 @@ class PagedAttention(Mixer):
                 ops.attention_decode(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
                                      att, Hq, Hkv, P, batch.max_context if batch.decode_only else batch.max_single_context,
                                      rows=None if batch.decode_only else batch.single_rows, err=ctx.err,
-                                     sink_score=self.sink_score, float_weights=True, softcap=self.softcap)
+                                     sink_score=self.sink_score, float_weights=self.weight_terms == 3,
+                                     softcap=self.softcap)
             if single < batch.S:
                 tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
                 ops.attention_prefill(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
                                       self.window, att, Hq, Hkv, P, err=ctx.err, min_rows=2 if single else 1,
                                       kernel="mma" if self.sink_score is not None else "auto",
-                                      sink_score=self.sink_score, weight_terms=3, softcap=self.softcap)
+                                      sink_score=self.sink_score, weight_terms=self.weight_terms, softcap=self.softcap)
         else:
             ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
                                         self.window, att, Hq, Hkv, D, Dv, sink_score=self.sink_score,

@@ -41,7 +41,11 @@ class LatentAttention(Mixer):
 
     ``own_kv`` False: the layer has no ``W_dkv`` and no norm of it; its call reads the pages of an earlier call (whose
     latent size, ``rot_dim`` and position encoding are the same) with its own ``W_uk``, ``W_uv``, queries and
-    window, and writes none."""
+    window, and writes none.
+
+    ``exact_weights`` False: a bfloat16 run rounds the softmax weights (computed in float32) to bfloat16 for their
+    product with the cached rows, as it rounds every other operand of a product, instead of taking them in as three
+    bfloat16 terms."""
 
     TC_HEADS_MIN_ROWS = 64      # steps of more rows make the per-head products on the tensor cores (bfloat16 runs)
 
@@ -51,7 +55,7 @@ class LatentAttention(Mixer):
     def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float,
                  eps: float, output_gate: bool = True, names: dict | None = None, rot_dim: int = 0,
                  position: PartSpec | None = None, window: int = 0, cache_window: int | None = None,
-                 gate_each: bool = False, own_kv: bool = True):
+                 gate_each: bool = False, own_kv: bool = True, exact_weights: bool = True):
         if min(heads, dim, vdim, q_rank, kv_rank) < 1 or rot_dim < 0 or window < 0:
             raise ValueError("latent attention: every size must be positive")
         if kv_rank + rot_dim > 512:
@@ -65,6 +69,7 @@ class LatentAttention(Mixer):
         if self.cache_window and (not self.window or self.cache_window < self.window):
             raise ValueError("latent attention: the pages must be kept for at least the layer's own window")
         self.gate_each, self.own_kv = bool(gate_each), bool(own_kv)
+        self.weight_terms = 3 if exact_weights else 1
         self.position = build_part("position", position) if isinstance(position, PartSpec) else position
         if self.R:
             if self.position is None or self.position.rotary_dim != self.R:
@@ -184,12 +189,12 @@ class LatentAttention(Mixer):
                                      self.window, lat, H, 1, P,
                                      batch.max_context if batch.decode_only else batch.max_single_context,
                                      rows=None if batch.decode_only else batch.single_rows, err=ctx.err,
-                                     float_weights=True)
+                                     float_weights=self.weight_terms == 3)
             if single < batch.S:
                 tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
                 ops.attention_prefill(q_lat, cache.k, cache.k, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
                                       self.window, lat, H, 1, P, err=ctx.err, min_rows=2 if single else 1,
-                                      weight_terms=3)
+                                      weight_terms=self.weight_terms)
         else:
             ops.paged_attention_general(q_lat, cache.k, None, bt, batch.row_entry, batch.positions, self.scale,
                                         self.window, lat, H, 1, P, P)

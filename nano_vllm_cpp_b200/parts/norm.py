@@ -61,8 +61,8 @@ class RMSNorm(Norm):
                 mix, inner = inner.as_tuple(), None
             elif isinstance(inner, (RowMix, BranchSum)):
                 inner = inner.sum()
-            ops.branch_norm_add(x, [] if inner is None else [inner], first.weight, first.eps, out, mix=mix,
-                                next_weight=self.weight, next_eps=self.eps, out32=None if out32 is out else out32)
+            ops.add_rmsnorm(x, inner, self.weight, self.eps, out, None if out32 is out else out32, mix=mix,
+                            branch_weight=first.weight, branch_eps=first.eps)
             return out, out32
         if isinstance(branch, RowMix):
             if branch.index.shape[1] <= ops.ADD_RMSNORM_MAX_MIX:

@@ -538,6 +538,13 @@ def test_a_layer_norms_what_goes_in_and_what_comes_out():
             ops.branch_norm_add(xd, [] if mixed else [f(y)], f(w1), 1e-5, out, mix=mix, next_weight=f(w2), next_eps=1e-6)
             close(xd, xn, 1e-5, "the stream")
             close(out, pg.rms(xn, 1e-6) * w2, 1e-5, "the next sublayer's input")
+            # the kernel that the layers run: the norm of the stream with the branch's own norm in front
+            for dt in (torch.float32, torch.bfloat16):
+                xd, out, out32 = f(x), torch.empty((T, H), dtype=dt, device=DEV), torch.empty((T, H), dtype=torch.float32, device=DEV)
+                ops.add_rmsnorm(xd, None if mixed else f(y), f(w2), 1e-6, out, out32, mix=mix, branch_weight=f(w1), branch_eps=1e-5)
+                close(xd, xn, 1e-5, "the stream")
+                close(out32, pg.rms(xn, 1e-6) * w2, 1e-5, "the next sublayer's input")
+                close(out, pg.rms(xn, 1e-6) * w2, 1e-5 if dt == torch.float32 else 1e-2, "the next sublayer's input as stored")
 
 
 # ------------------------------------------------------------------------------- whole models through the engine
