@@ -65,6 +65,8 @@ struct DecArgs {
   int* err;
   float scale;
   int q_dt, out_dt, q_stride, max_blocks, window, Hq, Hkv, D, page, splits, stages;
+  int same_kv;            // the values are read where the keys are (one array is both): the tensor-core form then
+                          // fetches a page once, and a stage of its ring is half as large
   float softcap;          // > 0: a scaled score s becomes softcap * tanh(s / softcap) (lane-per-chunk kernel only)
   int has_sink;           // the softmax's denominator also holds exp(sink): a key with that score and no value
   float sink;             // (the lane-per-chunk kernel and the merges add it; the tensor-core form does not know it)
@@ -384,7 +386,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   const int n_pages = max(0, min(p_hi, pb + per) - pb);
   const uint32_t box_bytes = (uint32_t)a.page * 128;           // one box: `page` keys x 64 elements
   const uint32_t half_stage = box_bytes * (D / 64);            // keys of one page; values follow
-  const uint32_t stage_bytes = 2 * half_stage;
+  const uint32_t stage_bytes = a.same_kv ? half_stage : 2 * half_stage;
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_k) : "memory");
@@ -447,7 +449,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
           tma_load_2d(st + c * box_bytes, &tm_k, &full_bar[s], c * 64, row);
-          tma_load_2d(st + half_stage + c * box_bytes, &tm_v, &full_bar[s], c * 64, row);
+          if (!a.same_kv) tma_load_2d(st + half_stage + c * box_bytes, &tm_v, &full_bar[s], c * 64, row);
         }
       }
     }
@@ -466,7 +468,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     for (int i = warp; i < n_pages; i += WARPS) {
       mbar_wait(&full_bar[s], ph, a.err, 0x7112);
       const uint32_t kbase = smem0 + (uint32_t)s * stage_bytes;
-      const uint32_t vbase = kbase + half_stage;
+      const uint32_t vbase = a.same_kv ? kbase : kbase + half_stage;
       const int j_page = (pb + i) * a.page;
       for (int kb = 0; kb < a.page / 16; ++kb) {
         const int j0 = j_page + kb * 16;
@@ -671,7 +673,7 @@ int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_p
   rc = nv_tensor_map_bf16(vc, rows, D, D, a.page, &tm_v);
   if (rc) return rc;
   a.scale = scale * 1.4426950408889634f;            // the kernel works in log2 units
-  const size_t ring = (size_t)a.stages * 2 * a.page * D * 2;
+  const size_t ring = (size_t)a.stages * (a.same_kv ? 1 : 2) * a.page * D * 2;
   const size_t merge = (size_t)WARPS * TC_ROWS * D * sizeof(float);
   const size_t smem = (ring > merge ? ring : merge) + 1024;
   static bool attr_done = false;
@@ -779,6 +781,15 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   // next page is on its way while it works on one (with one stage per warp a warp sat out the whole memory latency
   // between two pages), and three CTAs of 76 KB still share a multiprocessor.  Deeper rings lose CTAs and time.
   int tc_stages = stages / WARPS * WARPS;
+  a.same_kv = 0;
+  if (kc == vc && cache_dt == NV_DT_BF16) {        // one array is keys and values: a page is fetched once
+    long long s2 = (64 * 1024) / ((long long)page * D * esize);
+    if (s2 > MAX_STAGES) s2 = MAX_STAGES;
+    if (s2 / WARPS * WARPS >= WARPS) {
+      tc_stages = (int)(s2 / WARPS * WARPS);
+      a.same_kv = 1;
+    }
+  }
   if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS && !has_sink && !(softcap > 0.f)) {
     a.stages = tc_stages;
     // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head; with
@@ -794,6 +805,7 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
          : D == 192 ? launch_decode_tc<192, 1>(a, R, kc, vc, num_pages, scale, stream)
                     : launch_decode_tc<256, 1>(a, R, kc, vc, num_pages, scale, stream);
   } else if (cache_dt == NV_DT_BF16) {
+    a.same_kv = 0;
     rc = D <= 64 ? launch_decode<bf16, 1>(a, R, G, smem, stream)
                  : (D <= 128 ? launch_decode<bf16, 2>(a, R, G, smem, stream)
                              : launch_decode<bf16, 4>(a, R, G, smem, stream));

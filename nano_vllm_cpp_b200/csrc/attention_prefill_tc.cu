@@ -44,6 +44,10 @@ struct PtArgs {
   bf16* out;
   int* err;
   float scale_log2;         // scale * log2(e)
+  float softcap, cap_in;    // softcap > 0: a score s becomes softcap * tanh(s * cap_in), cap_in = scale / softcap
+                            // (scale_log2 is then log2(e) alone)
+  int has_sink;             // the softmax's denominator also holds exp(sink): a key with that score and no value
+  float sink_log2;          // the sink's score times log2(e)
   int S, max_blocks, window, Hq, Hkv, page;
   int min_rows;             // entries with fewer rows are left to another kernel
   int first_wave;           // CTAs that start alone on a multiprocessor (their number), before the second ones join them
@@ -244,6 +248,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         tmem_ld32_nowait(tmem_s + (i & 1) * TKB + lane_off + 32, s + 32);
         tmem_ld_wait();
         tmem_ld_fence<64>(s);
+        if (a.softcap > 0.f) {
+#pragma unroll
+          for (int c = 0; c < TKB; ++c) s[c] = a.softcap * tanhf(s[c] * a.cap_in);
+        }
         if (!live || j0 + TKB - 1 > p_row || j0 < w_lo) {
 #pragma unroll
           for (int c = 0; c < TKB; ++c)
@@ -326,6 +334,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       // ---- the result: O / l
       mbar_wait(&pv_done, (n_blocks - 1) & 1, a.err, 0x7208);
       tc_fence_after();
+      if (a.has_sink) l += exp2f(a.sink_log2 - (m == -INFINITY ? 0.f : m * a.scale_log2));   // relative to the sums' reference
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -390,14 +399,21 @@ NV_API int nv_attention_prefill_tc_usable(int D, int page) {
 NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const void* kc, const void* vc, int num_pages,
                                    const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                    int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,
-                                   int page, int min_rows, int weight_terms, int* err, cudaStream_t stream) {
+                                   int page, int min_rows, int weight_terms, int* err, int has_sink, float sink_score,
+                                   float softcap, cudaStream_t stream) {
+  // has_sink: a further key with the score sink_score and no value in every softmax.  softcap > 0: a scaled score s
+  // becomes softcap * tanh(s / softcap) before mask and softmax.
   if (!nv_attention_prefill_tc_usable(D, page) || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
   if (weight_terms != 1 && weight_terms != 3) return NV_ERR_UNSUPPORTED;
   if (q_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0 || T == 0) return NV_OK;
   PtArgs a;
   a.block_table = block_table; a.cu_rows = cu_rows; a.entry_pos0 = entry_pos0; a.out = (bf16*)out; a.err = err;
-  a.scale_log2 = scale * 1.4426950408889634f;
+  a.scale_log2 = (softcap > 0.f ? 1.f : scale) * 1.4426950408889634f;
+  a.softcap = softcap > 0.f ? softcap : 0.f;
+  a.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+  a.has_sink = has_sink ? 1 : 0;
+  a.sink_log2 = sink_score * 1.4426950408889634f;
   a.S = S; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.page = page;
   a.min_rows = min_rows;
   static int num_sms = 0;

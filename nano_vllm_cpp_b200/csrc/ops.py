@@ -450,8 +450,8 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     128 and pages of 16, 32 or 64 keys, else the mma.sync kernel (``kernel="mma"`` asks for that one).  Entries
     with fewer than ``min_rows`` rows are skipped and their rows of ``out`` left as they are.
     ``weight_terms`` = 3: the float32 weights enter the product with the values as three bfloat16 terms, all their
-    bits (either kernel).  ``sink_score`` (a further key with that score and no value in every softmax) is the
-    mma.sync kernel's."""
+    bits (either kernel).  ``sink_score``: a further key with that score and no value in every softmax; ``softcap``
+    > 0: a scaled score s becomes ``softcap * tanh(s / softcap)`` before mask and softmax (either kernel)."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, out)
     _i32(block_table, cu_rows, entry_pos0)
     _need(qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -462,14 +462,13 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     page = k_cache.shape[2]
     _need(kernel in ("auto", "mma"), "attention_prefill: kernel is 'auto' or 'mma'")
     _need(weight_terms in (1, 3), "attention_prefill: the weights are one bfloat16 term or three")
-    if sink_score is not None or softcap > 0:     # (capped scores, s -> softcap * tanh(s / softcap), are the mma.sync kernel's too)
-        kernel = "mma"
     if kernel == "auto" and L.nv_attention_prefill_tc_usable(D, page):
         _check(L.nv_attention_prefill_tc(_p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache),
                                          k_cache.shape[0], _p(block_table), block_table.shape[1],
                                          _p(cu_rows), _p(entry_pos0), S, max_tiles, scale,
                                          window, _p(out), Hq, Hkv, D, page,
                                          min_rows, weight_terms, _p(err.t if err is not None else _global_err().t),
+                                         (0 if sink_score is None else 1), float(sink_score or 0.0), float(softcap),
                                          _stream()),
                "attention_prefill_tc")
         return

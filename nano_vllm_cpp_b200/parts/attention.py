@@ -220,7 +220,7 @@ class PagedAttention(Mixer):
                 tiles = (batch.T - single) // ops.attention_prefill_tile_rows() + (batch.S - single)
                 ops.attention_prefill(q, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
                                       self.window, att, Hq, Hkv, P, err=ctx.err, min_rows=2 if single else 1,
-                                      kernel="mma" if self.sink_score is not None else "auto",
+                                      kernel="mma" if self.sink_score is not None and self.weight_terms == 3 else "auto",
                                       sink_score=self.sink_score, weight_terms=self.weight_terms, softcap=self.softcap)
         else:
             ops.paged_attention_general(q, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,

@@ -48,6 +48,7 @@ def _call(lib, name, qkv, kc, vc, bt, ent, pos, out, Hq, Hkv, D, page, splits, s
         args.append(c_void_p(0))            # the ordinary entry point also takes an error flag; none here
         args += [c_void_p(0), c_int(0)]     # ... and counters for adding the splits up in the kernel itself; none
         args += [c_int(0), c_float(0.0), c_int(0)]      # ... no sink in the softmax, weights as the kernel likes them
+        args.append(c_float(0.0))                       # ... and scores that are not capped
     args.append(stream)
     return fn(*args)
 
