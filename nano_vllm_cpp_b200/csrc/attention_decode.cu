@@ -771,6 +771,13 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   // the last blocks' sums lengthen the kernel's tail by more than the second kernel's launch costs (measured per
   // decode step: batch 1 507 -> 511 tokens/s, batch 8 2,209 -> 2,212, batch 64 6,252 -> 6,192).
   a.split_count = (split_count && (long long)R * Hq <= split_count_len && R * Hq <= 256) ? split_count : nullptr;
+  // ... and only while the last block's sum is short: a thread of it adds its outputs one after the other, each a chain
+  // of loads from the second-level cache, so with sixteen heads of 256 elements on one kv head (4,096 outputs for 160
+  // threads) that one block ran for 50 of the kernel's 64 us; the second kernel has a block per row and head.
+  {
+    const int heads_per_block = Hq / Hkv < 16 ? Hq / Hkv : 16;
+    if ((long long)heads_per_block * D > 1024) a.split_count = nullptr;
+  }
   a.stages = stages;
   const size_t smem = (size_t)stages * 2 * page * D * esize;
   const int G = Hq / Hkv;
