@@ -23,7 +23,11 @@
 // issuer adds three products P_t(i) V(i) into the same accumulator.  The three tiles take 48 KB, so with a head size
 // of 128 one CTA lives on a multiprocessor instead of two.
 //
-// Takes bfloat16, head_dim 64 or 128, pages of 16, 32 or 64 keys; everything else goes to the mma.sync kernel
+// A head size of 256 (the cached rows of latent attention: one shared kv head, keys and values the same rows) takes
+// 384 columns of tensor memory and 177 KB of shared memory (209 KB with three terms), so one CTA lives on a
+// multiprocessor.
+//
+// Takes bfloat16, head_dim 64, 128 or 256, pages of 16, 32 or 64 keys; everything else goes to the mma.sync kernel
 // (attention_prefill.cu), which is also this kernel's twin in the tests.  (The reference's kernel:
 // src/hip_ops.hip:473-551.)
 #include "tcgen05.cuh"
@@ -60,8 +64,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Columns of tensor memory a CTA takes: two S buffers of 64 and O of D columns, rounded up to a power of two.
+template <int D>
+constexpr int pt_tmem_cols() { return 2 * TKB + D <= 256 ? 256 : 512; }
+
 template <int D, int TERMS>
-__global__ void __launch_bounds__(PT_THREADS, 2)
+__global__ void __launch_bounds__(PT_THREADS, D <= 128 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                             const __grid_constant__ CUtensorMap tm_v, PtArgs a) {
   constexpr int SL = D / 64;                       // 64-element slabs of the head dimension
@@ -112,7 +120,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   // their probabilities are zero, and zero times whatever the shared memory held before must be zero
   for (int i = tid; i < (int)(3 * SL * KV_SLAB / 16); i += PT_THREADS) ((uint4*)Ks)[i] = make_uint4(0, 0, 0, 0);
   fence_async_smem();
-  if (warp == 1) tmem_alloc(&tmem_base_s, 256);
+  if (warp == 1) tmem_alloc(&tmem_base_s, pt_tmem_cols<D>());
   grid_dep_wait();              // queries, and this step's keys and values, come from the kernel before
   grid_dep_launch();
   if (tid == 0) {               // which (entry, tile of 128 rows) is this CTA's?  later tiles (more keys) first
@@ -358,7 +366,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 256);
+  if (warp == 1) tmem_dealloc(tmem_base, pt_tmem_cols<D>());
 }
 
 template <int D, int TERMS>
@@ -389,7 +397,7 @@ int launch_prefill_tc(const PtArgs& a, const void* qkv, int q_stride, int T, con
 }  // namespace
 
 NV_API int nv_attention_prefill_tc_usable(int D, int page) {
-  return (D == 64 || D == 128) && (page == 16 || page == 32 || page == 64);
+  return (D == 64 || D == 128 || D == 256) && (page == 16 || page == 32 || page == 64);
 }
 
 // Same contract as nv_attention_prefill (max_tiles counts tiles of nv_attention_prefill_tile_rows() = 64 rows, an
@@ -427,8 +435,10 @@ NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const v
   const int tiles = (max_tiles + S + 1) / 2;
   if (weight_terms == 3) {
     if (D == 64) return launch_prefill_tc<64, 3>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
+    if (D == 256) return launch_prefill_tc<256, 3>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
     return launch_prefill_tc<128, 3>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
   }
   if (D == 64) return launch_prefill_tc<64, 1>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
+  if (D == 256) return launch_prefill_tc<256, 1>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
   return launch_prefill_tc<128, 1>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
 }

@@ -248,7 +248,9 @@ LATENTS = [pg.latent_layer(heads=3, dim=24, rot_dim=8, vdim=40, q_rank=20, kv_ra
            pg.latent_layer(heads=4, dim=32, rot_dim=16, vdim=48, q_rank=48, kv_rank=48, scale=0.17),               # rows of 64
            pg.latent_layer(heads=8, dim=64, rot_dim=32, vdim=48, q_rank=72, kv_rank=96, scale=0.125, window=33),   # rows of 128
            pg.latent_layer(heads=2, dim=4, rot_dim=48, vdim=8, q_rank=16, kv_rank=16, scale=0.3, base=100.0),      # the turned part weighs most
-           pg.latent_layer(heads=5, dim=8, rot_dim=4, vdim=72, q_rank=4, kv_rank=260, scale=0.3, window=500)]
+           pg.latent_layer(heads=5, dim=8, rot_dim=4, vdim=72, q_rank=4, kv_rank=260, scale=0.3, window=500),
+           pg.latent_layer(heads=4, dim=64, rot_dim=64, vdim=64, q_rank=64, kv_rank=192, scale=0.09),              # rows of 256
+           pg.latent_layer(heads=3, dim=32, rot_dim=32, vdim=40, q_rank=32, kv_rank=224, scale=0.12, window=70)]
 
 
 @pytest.mark.parametrize("fast", [True, False])
@@ -267,7 +269,7 @@ def test_latent_attention_alone(dtype, layer, fast):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows", [[300, 101]])
-@pytest.mark.parametrize("layer", [LATENTS[3], LATENTS[4], LATENTS[0]])
+@pytest.mark.parametrize("layer", [LATENTS[3], LATENTS[4], LATENTS[0], LATENTS[7], LATENTS[8]])
 def test_latent_attention_steps_of_many_rows(dtype, layer, rows):
     """Steps of hundreds of rows, alone and beside single rows: a bfloat16 run makes the per-head products of such
     steps another way (head by head on the tensor cores where the sizes allow) than those of a few rows."""
