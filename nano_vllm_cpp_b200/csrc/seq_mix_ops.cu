@@ -587,7 +587,7 @@ __global__ void __launch_bounds__(QK_THREADS) qk_prepare_store_kernel(QkArgs a) 
 // across heads are linear in the queries, so the mixing is done once per row on the queries); values are read from
 // the head's own kv head as always.  Chunks of ATTG_THREADS keys, running maximum.
 constexpr int ATTG_THREADS = 128;
-constexpr int ATTG_NV = 4;           // output elements per thread: values up to ATTG_NV * ATTG_THREADS wide
+constexpr int ATTG_NV = 8;           // output elements per thread: values up to ATTG_NV * ATTG_THREADS wide
 
 __global__ void __launch_bounds__(ATTG_THREADS) paged_attention_general_kernel(
     const void* __restrict__ q, int q_dt, const void* __restrict__ kc, const void* __restrict__ vc, int cache_dt,

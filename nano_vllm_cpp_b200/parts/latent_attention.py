@@ -58,8 +58,8 @@ class LatentAttention(Mixer):
                  gate_each: bool = False, own_kv: bool = True, exact_weights: bool = True):
         if min(heads, dim, vdim, q_rank, kv_rank) < 1 or rot_dim < 0 or window < 0:
             raise ValueError("latent attention: every size must be positive")
-        if kv_rank + rot_dim > 512:
-            raise ValueError(f"a cached row of {kv_rank + rot_dim} elements is not supported: the attention kernel takes up to 512")
+        if kv_rank + rot_dim > 1024:
+            raise ValueError(f"a cached row of {kv_rank + rot_dim} elements is not supported: the attention kernel takes up to 1024")
         self.hidden, self.H, self.D, self.Dv, self.rq, self.rk = hidden_size, heads, dim, vdim, q_rank, kv_rank
         self.scale, self.eps, self.output_gate = float(scale), float(eps), bool(output_gate)
         self.names = dict(self._NAMES, **(names or {}))
