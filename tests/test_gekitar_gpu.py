@@ -284,6 +284,39 @@ def test_latent_attention_steps_of_many_rows(dtype, layer, rows):
         close(got[i], plain_latent(x, W, layer, eps), PART_TOL[dtype], f"request {i}")
 
 
+@pytest.mark.parametrize("kv_rank,rot_dim,window", [(8, 8, 0), (24, 8, 5), (32, 16, 0), (64, 16, 30), (64, 32, 0), (96, 16, 40),
+                                                    (128, 32, 96), (160, 32, 0), (128, 64, 50), (192, 32, 0), (224, 16, 33),
+                                                    (200, 56, 0), (320, 64, 20), (500, 76, 0)])
+def test_cached_rows_of_many_sizes(kv_rank, rot_dim, window):
+    """A bfloat16 run picks its attention kernels by the size of the cached row (tcgen05, mma.sync or the general one
+    for portions; tensor-core, lane-per-chunk or the general one for single rows): every multiple of sixteen up to
+    256 in turn, and rows beyond, in portions beside single rows."""
+    width, eps = 64, 1e-5
+    layer = pg.latent_layer(heads=3, dim=24, rot_dim=rot_dim, vdim=32, q_rank=16, kv_rank=kv_rank, scale=0.2, window=window)
+    W = pg.mixer_weights(layer, width, 61)
+    parts, cache, ctx = mixers_setup([layer], width, [W], torch.bfloat16, eps=eps)
+    xs = inputs(width, [66, 51], 62)
+    got = run_cut(parts, cache, xs, CUTS, torch.bfloat16, PAGES, ctx)[0]
+    for i, x in enumerate(xs):
+        close(got[i], plain_latent(x, W, layer, eps), PART_TOL[torch.bfloat16], f"request {i}")
+
+
+@pytest.mark.parametrize("dim,vdim,heads,kv_heads", [(16, 16, 4, 2), (48, 32, 2, 2), (64, 128, 4, 1), (80, 80, 3, 1), (96, 64, 6, 3),
+                                                     (128, 64, 8, 2), (192, 192, 2, 1), (256, 256, 2, 2), (256, 128, 4, 2)])
+def test_attention_heads_of_many_sizes(dim, vdim, heads, kv_heads):
+    """The same for the attention with sink and cap: a bfloat16 run pads keys and values to one head size and picks
+    its kernels by it."""
+    width, eps = 64, 1e-5
+    layer = pg.sink_layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, rot_dims=dim // 2, base=1e4, scale=2.0 / dim,
+                          softcap=6.0, scaling=YARN)
+    W = pg.mixer_weights(layer, width, 63)
+    parts, cache, ctx = mixers_setup([layer], width, [W], torch.bfloat16, eps=eps)
+    xs = inputs(width, [66, 51], 64)
+    got = run_cut(parts, cache, xs, CUTS, torch.bfloat16, PAGES, ctx)[0]
+    for i, x in enumerate(xs):
+        close(got[i], pg.sink_attention(x, W, "m.", layer["mixer"], eps), PART_TOL[torch.bfloat16], f"request {i}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("own,w1,w2", [(24, 40, 9), (0, 30, 1), (17, 17, 64)])
 def test_latents_of_another_layer(dtype, own, w1, w2):
@@ -625,6 +658,105 @@ def test_unequal_requests_together_with_pages_used_again(name, dtype, models):
     for r, n in L.items():
         assert at[r] == n
         check_rows(st, models, name, r, ids[r], dtype, f"{name} request {r}")
+
+
+def drawn_config(rng):
+    """A model of four to nine layers whose kinds, order and sizes are drawn: every mixer kind at least once, up to two
+    sets of sizes per kind, windowed latent layers that read an earlier latent layer's pages where one with the same
+    latent fits, every feed-forward kind and layers without one, sizes that do and do not fit the tensor-core
+    kernels."""
+    width = rng.choice([128, 192, 256, 320])
+    n = rng.randint(4, 9)
+    kinds = [rng.choice(["latent", "window", "attn"]) for _ in range(n)]
+    for must in ("latent", "window", "attn"):
+        if must not in kinds:
+            kinds[rng.randrange(n)] = must
+
+    def latent():
+        return dict(heads=rng.choice([2, 4, 6, 8, 12]), dim=rng.choice([16, 32, 48, 64]), vdim=rng.choice([32, 48, 64, 80]),
+                    q_rank=rng.choice([48, 64, 96]), scale=rng.choice([0.125, 0.1, 0.18]))
+
+    def kept():       # what two layers must share to share pages
+        return dict(kv_rank=rng.choice([48, 64, 96, 112, 160, 192]), rot_dim=rng.choice([16, 32, 64]),
+                    base=rng.choice([1e4, 2e4, 2.5e5]))
+
+    def attn():
+        kv, dim = rng.choice([1, 2, 3, 4]), rng.choice([32, 64, 96, 128])
+        return dict(heads=kv * rng.choice([1, 2, 3, 4]), kv_heads=kv, dim=dim, vdim=rng.choice([32, 64, 96, 128]),
+                    rot_dims=rng.choice([16, 32, dim]), base=rng.choice([1e4, 1e6, 100.0]), scale=rng.choice([0.125, 0.09, 0.2]),
+                    softcap=rng.choice([10.0, 20.0, 50.0]),
+                    scaling=rng.choice([None, {"factor": 8.0, "original": 128, "fast": 32.0, "slow": 1.0}, YARN]))
+
+    def mlp():
+        k = rng.choice(["dense", "moe", "moe", "none"])
+        if k == "dense":
+            return pg.dense_ff(rng.choice([128, 256, 320]), rng.choice([1.0, 1.5, 7.0]))
+        if k == "moe":
+            e = rng.choice([4, 8, 12])
+            return pg.moe_ff(e, rng.choice([1, 2, 3, e]), rng.choice([32, 64, 96]), rng.choice([0, 64, 96, 128]))
+        return None
+
+    latents, keeps, attns = [latent(), latent()], [kept(), kept()], [attn(), attn()]
+    layers, owners = [], {}                 # owners: which layer first made the latents of kept set k
+    for at, k in enumerate(kinds):
+        i = rng.randrange(2)
+        if k == "attn":
+            layers.append(pg.sink_layer(mlp=mlp(), kind="attention" if i == 0 else "attention_2", **attns[i]))
+            continue
+        j = rng.randrange(2)
+        window = rng.choice([17, 40, 64, 96, 150]) if k == "window" else 0
+        src = owners.get(j) if (k == "window" and rng.random() < 0.6) else None
+        if src is None:
+            owners.setdefault(j, at)
+        kind = ("latent_attention_2" if k == "window" else "latent_attention") + ("" if i == 0 else "_3")
+        layers.append(pg.latent_layer(window=window, kv_from=src, mlp=mlp(), kind=kind, **latents[i], **keeps[j]))
+    return pg.model_config(layers, width=width, vocab=rng.choice([300, 512, 1000]), eps=rng.choice([1e-6, 1e-5]),
+                           embed_scale=rng.choice([None, 4.0, 16.0]))
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_drawn_models_in_a_mixed_schedule(seed, tmp_path):
+    """Drawn models, both dtypes: five unequal requests on three slots and 576 tokens of pages, portions of up to 150
+    tokens beside single rows of others, decoding over dozens of steps, finished requests' pages and slots used
+    again; every request's logits equal the plain implementation's of the request alone."""
+    import random
+    cfg = drawn_config(random.Random(seed))
+    W = pg.random_weights(cfg, seed)
+    one = {"F": (cfg, W, pg.write_folder(cfg, W, str(tmp_path)))}
+    L = {"a": 230, "b": 90, "c": 170, "d": 45, "e": 120}
+    g = torch.Generator().manual_seed(seed)
+    ids = {r: [int(t) for t in torch.randint(0, cfg["vocab"], (n,), generator=g)] for r, n in L.items()}
+    for dtype in ("float32", "bfloat16"):
+        st = Steps(make_runner(one["F"][2], dtype, 576, max_requests=3))
+        at = {r: 0 for r in L}
+
+        def take(r, n):
+            toks = ids[r][at[r]:at[r] + n]
+            at[r] += len(toks)
+            return (r, toks)
+
+        def done(*rs):
+            return [r for r in rs if at[r] == L[r]]
+
+        st.step([take("a", 150), take("b", 2)])
+        st.step([take("a", 1), take("b", 88), take("c", 3)], end=done("b"))
+        for _ in range(30):
+            st.step([take("a", 1), take("c", 1)])
+        st.step([take("a", 49), take("c", 2), take("d", 45)], end=done("a", "d"))
+        st.step([take("c", 135), take("e", 7)], end=done("c"))
+        for _ in range(40):
+            st.step([take("e", 1)])
+        st.step([take("e", 73)], end=done("e"))
+        for r, n in L.items():
+            assert at[r] == n
+            want, margins = plain_logits(one, "F", ids[r])
+            # (a drawn router may put many rows near an edge: what is held is every row before the first of them)
+            got = st.rows(r, n)
+            upto = n
+            if dtype == "bfloat16" and bool((margins < EDGE).any()):
+                upto = int(torch.nonzero(margins < EDGE)[0])
+            if upto:
+                close(got[:upto], want[:upto], TOL[dtype], f"seed {seed} {dtype} request {r}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
