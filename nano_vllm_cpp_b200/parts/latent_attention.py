@@ -118,7 +118,7 @@ class LatentAttention(Mixer):
         self.w_out = fetch(n["o"])
         # A bfloat16 run with many rows makes the two small products per head on the tensor cores, all heads in one
         # launch (``ops.gemm_fast_heads``: a tile per token tile and head): the weights as [out, in] per head.
-        self._tiles, self._tiles_kept = {}, set()
+        self._tiles = {}
         self.tc_heads = (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and uk.dtype == torch.bfloat16
                          and (D + R) % 8 == 0 and Dv % 8 == 0 and rk % 8 == 0 and P % 8 == 0)
         if self.tc_heads:
@@ -126,17 +126,13 @@ class LatentAttention(Mixer):
             self.w_uv_n = uv.contiguous()                                            # [h][v][r] over the latent's part of a row
 
     def _head_tiles(self, T, dev):
-        """The tile list of the per-head products for a step of T rows; lists made while a step is captured are
-        named by address in its graph and stay."""
+        """The tile list of the per-head products for a step of T rows.  Lists are kept for good (a few hundred bytes
+        per row count): a captured step names its list by address, and making one copies from the host, which a
+        capture does not allow; a shape is captured the second time it is seen, so its list exists by then."""
         key = (T, torch.device(dev))
         tl = self._tiles.get(key)
         if tl is None:
-            loose = [k for k in self._tiles if k not in self._tiles_kept]
-            if len(loose) >= 64:
-                self._tiles.pop(loose[0])
             tl = self._tiles[key] = ops.HeadTiles(T, self.H, dev)
-        if torch.cuda.is_current_stream_capturing():
-            self._tiles_kept.add(key)
         return tl
 
     def cache_spec(self):

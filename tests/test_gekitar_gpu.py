@@ -615,6 +615,26 @@ def test_prompt_then_token_by_token(name, dtype, models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P", "R"])
+def test_steps_of_one_shape_are_replayed(name, dtype, models):
+    """Five requests in turn, each as a portion of 100 tokens and a portion of 30 beside a single row of the request
+    before: from its second occurrence on a shape runs as a captured graph, the per-head products of many rows and the
+    mixtures' permutation buffers among its kernels."""
+    runner = make_runner(models[name][2], dtype, 512)
+    st = Steps(runner)
+    all_ids = [ids_for(name, 131, salt=40 + k) for k in range(5)]
+    for k, ids in enumerate(all_ids):
+        st.step([(f"g{k}", ids[:100])])
+        parts = [(f"g{k}", ids[100:130])]
+        if k:
+            parts.append((f"g{k - 1}", all_ids[k - 1][130:131]))
+        st.step(parts, end=[f"g{k - 1}"] if k else [])
+    st.step([("g4", all_ids[4][130:131])], end=["g4"])
+    for k, ids in enumerate(all_ids):
+        check_rows(st, models, name, f"g{k}", ids, dtype, f"{name} request {k}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", NAMES)
 def test_portions_of_several_sizes(name, dtype, models):
     runner = make_runner(models[name][2], dtype, 256)
